@@ -1,2 +1,2 @@
 from .manager import (CacheError, CacheLayout, CacheManager, OutOfPages, OutOfSlots, PageGroup,  # noqa: F401
-                      layout_of)
+                      cache_key, layout_of)

@@ -61,12 +61,28 @@ class CacheLayout:
         raise KeyError(f"cache {cache_id} holds no pages")
 
 
+def cache_key(cache_id: int, name: str = ""):
+    """How a named part of what a run-order entry keeps is called in a layout: the entry's cache id alone for
+    the unnamed one (a mixer with a single need), else ``(cache id, name)``."""
+    return (cache_id, name) if name else cache_id
+
+
 def layout_of(cache_specs: Dict[int, object]) -> CacheLayout:
-    """``cache_specs``: cache id -> PagedCacheSpec | StateSpec | None (what each mixer asked for)."""
+    """``cache_specs``: cache id -> PagedCacheSpec | StateSpec | None (what each mixer asked for), or a dict
+    name -> one of these for a layer that keeps several things per request (the keys of its attention and the
+    last input of a shift; a recurrence's state and the tail of its convolution): each is then filed under
+    ``cache_key(cache id, name)``."""
     layout = CacheLayout()
     by_spec: Dict[PagedCacheSpec, PageGroup] = {}
+    flat = {}
     for cache_id in sorted(cache_specs):
-        spec = cache_specs[cache_id]
+        need = cache_specs[cache_id]
+        if isinstance(need, dict):
+            for name in sorted(need):
+                flat[cache_key(cache_id, name)] = need[name]
+        else:
+            flat[cache_id] = need
+    for cache_id, spec in flat.items():
         if spec is None:
             continue
         if isinstance(spec, StateSpec):

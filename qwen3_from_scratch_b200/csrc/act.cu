@@ -10,7 +10,7 @@ namespace q3 {
 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total,
-                              int interleave8) {
+                              int interleave8, int act) {
   pdl_wait();
   pdl_launch_dependents();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -22,12 +22,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   const int up_col = interleave8 ? gate_col + 8 : I + i;
   const float g = to_float(row[gate_col]);
   const float u = to_float(row[up_col]);
-  out[idx] = from_float<T>(u * (g / (1.0f + expf(-g))));
+  out[idx] = from_float<T>(u * activate(g, act));
 }
 
 // Eight outputs per thread with 16-byte accesses (bfloat16, I a multiple of 8).
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                                     int I, size_t total8, int interleave8) {
+                                     int I, size_t total8, int interleave8, int act) {
   pdl_wait();
   pdl_launch_dependents();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -44,7 +44,7 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, 
   for (int k = 0; k < 4; ++k) {
     const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
     const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
-    __nv_bfloat162 o = __floats2bfloat162_rn(u0 * (g0 / (1.0f + expf(-g0))), u1 * (g1 / (1.0f + expf(-g1))));
+    __nv_bfloat162 o = __floats2bfloat162_rn(u0 * activate(g0, act), u1 * activate(g1, act));
     ow[k] = *reinterpret_cast<uint32_t*>(&o);
   }
   *reinterpret_cast<uint4*>(out + t * (size_t)I + 8 * j) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
@@ -53,8 +53,10 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, 
 }  // namespace q3
 
 // gate_up: [T, 2I]; out: [T, I]; both in `dtype`.  interleave8: columns 16j..16j+7 gate, 16j+8..16j+15 up.
-extern "C" int q3_swiglu(const void* gate_up, void* out, int dtype, int T, int I, int interleave8,
-                         cudaStream_t stream) {
+// act: Q3_ACT_SILU, Q3_ACT_RELU or Q3_ACT_GELU_TANH, applied to the gate.
+extern "C" int q3_gated_act(const void* gate_up, void* out, int dtype, int T, int I, int interleave8, int act,
+                            cudaStream_t stream) {
+  if (act < Q3_ACT_SILU || act > Q3_ACT_GELU_TANH) return Q3_ERR_SIZE;
   if (T <= 0 || I <= 0) return 0;
   if (interleave8 && I % 8) return Q3_ERR_SIZE;
   const size_t total = (size_t)T * I;
@@ -64,15 +66,20 @@ extern "C" int q3_swiglu(const void* gate_up, void* out, int dtype, int T, int I
   if (dtype == Q3_BF16 && I % 8 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0) {
     const size_t total8 = total / 8;
     q3::launch(q3::swiglu_bf16x8_kernel, dim3((unsigned)((total8 + threads - 1) / threads)), dim3(threads), 0, stream, 
-        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total8, interleave8);
+        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total8, interleave8, act);
     return q3::launch_status();
   }
   if (dtype == Q3_F32)
-    q3::launch(q3::swiglu_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total, interleave8);
+    q3::launch(q3::swiglu_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total, interleave8, act);
   else if (dtype == Q3_BF16)
     q3::launch(q3::swiglu_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, 
-        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total, interleave8);
+        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total, interleave8, act);
   else
     return Q3_ERR_DTYPE;
   return q3::launch_status();
+}
+
+extern "C" int q3_swiglu(const void* gate_up, void* out, int dtype, int T, int I, int interleave8,
+                         cudaStream_t stream) {
+  return q3_gated_act(gate_up, out, dtype, T, I, interleave8, Q3_ACT_SILU, stream);
 }

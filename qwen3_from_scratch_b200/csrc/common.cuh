@@ -80,6 +80,28 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return warp_sum(t);
 }
 
+// Activations by code, as the C ABI names them: what multiplies the "up" half of a gated feed-forward,
+// and what a short convolution applies to its output.  Evaluated in float32.
+#define Q3_ACT_SILU 0
+#define Q3_ACT_RELU 1
+#define Q3_ACT_GELU_TANH 2
+#define Q3_ACT_NONE 3
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float sigmoid_f(float g) { return 1.0f / (1.0f + expf(-g)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float activate(float g, int act) {
+  switch (act) {
+    case Q3_ACT_SILU: return silu_f(g);
+    case Q3_ACT_RELU: return fmaxf(g, 0.f);
+    case Q3_ACT_GELU_TANH: return gelu_tanh_f(g);
+    default: return g;
+  }
+}
+
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Streaming multiprocessors of the current device (asked once per device; grids, split counts and the

@@ -232,6 +232,116 @@ __global__ void rmsnorm_rows_kernel(const T* __restrict__ x, const float* __rest
   for (int i = lane; i < dim; i += 32) dst[i] = from_float<T>(to_float(src[i]) * rs * w[i]);
 }
 
+// ---------------------------------------------------------------- norm after the sum
+// resid[r, :] = rmsnorm(alpha * resid[r, :] + delta[r, :]) * w, in place in the float32 stream; `out`, if
+// given, receives the same row in the compute dtype (the operand of the next matrix product).  The
+// arrangement of a block that norms after each sub-layer's sum instead of before the sub-layer.
+template <typename T>
+__global__ void scale_add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                         const float* __restrict__ w, T* __restrict__ out, int H, float alpha,
+                                         float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
+  extern __shared__ float row_buf[];
+  __shared__ float scratch[32];
+  float* r = resid + (size_t)blockIdx.x * H;
+  const T* d = delta ? delta + (size_t)blockIdx.x * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = alpha * r[i];
+    if (d) v += to_float(d[i]);
+    row_buf[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+  T* o = out ? out + (size_t)blockIdx.x * H : nullptr;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float y = row_buf[i] * rs * w[i];
+    r[i] = y;
+    if (o) o[i] = from_float<T>(y);
+  }
+}
+
+// The same with one warp per row and the row in registers (widths that are multiples of 128, up to 2048).
+template <typename T, int NCH>
+__global__ void __launch_bounds__(NW_WARPS * 32)
+scale_add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ w,
+                              T* __restrict__ out, int n_rows, float alpha, float eps) {
+  constexpr int H = NCH * 128;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * NW_WARPS + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  float* r = resid + (size_t)row * H;
+  float v[NCH][4];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    Vec4<float>::load(r + (i * 32 + lane) * 4, v[i]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[i][k] *= alpha;
+  }
+  if (delta) {
+    const T* d = delta + (size_t)row * H;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      float dv[4];
+      Vec4<T>::load(d + (i * 32 + lane) * 4, dv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[i][k] += dv[k];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) ss += v[i][k] * v[i][k];
+  ss = warp_sum(ss);
+  const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    float wv[4];
+    Vec4<float>::load(w + (i * 32 + lane) * 4, wv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[i][k] = v[i][k] * rs * wv[k];
+    Vec4<float>::store(r + (i * 32 + lane) * 4, v[i]);
+    if (out) Vec4<T>::store(out + (size_t)row * H + (i * 32 + lane) * 4, v[i]);
+  }
+}
+
+template <typename T>
+static int scale_add_rmsnorm_launch(float* resid, const void* delta, const float* w, void* out, int n_rows, int H,
+                                    float alpha, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return Q3_ERR_SIZE;
+  const bool vec = ((uintptr_t)resid % 16 == 0) && ((uintptr_t)w % 16 == 0) && (!out || (uintptr_t)out % 16 == 0) &&
+                   (!delta || (uintptr_t)delta % 16 == 0);
+  // bfloat16 only: the float32 path keeps one kernel, and so one order of summation, for every number of rows
+  if (vec && sizeof(T) == 2 && H % 128 == 0 && H <= 2048) {
+    switch (H / 128) {
+#define Q3_NW(N) case N: q3::launch(scale_add_rmsnorm_warp_kernel<T, N>, dim3((n_rows + NW_WARPS - 1) / NW_WARPS), \
+                                   dim3(NW_WARPS * 32), 0, stream, resid, (const T*)delta, w, (T*)out, n_rows, alpha, eps); break;
+      Q3_NW(1) Q3_NW(2) Q3_NW(3) Q3_NW(4) Q3_NW(5) Q3_NW(6) Q3_NW(7) Q3_NW(8)
+      Q3_NW(9) Q3_NW(10) Q3_NW(11) Q3_NW(12) Q3_NW(13) Q3_NW(14) Q3_NW(15) Q3_NW(16)
+#undef Q3_NW
+    }
+    note_stream_written();
+    return launch_status();
+  }
+  int threads = ((H + 31) / 32) * 32;
+  if (threads > 512) threads = 512;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(scale_add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  q3::launch(scale_add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, resid, (const T*)delta, w, (T*)out, H,
+             alpha, eps);
+  note_stream_written();
+  return launch_status();
+}
+
 template <typename T>
 static int add_rmsnorm_launch(float* resid, const void* delta, const float* w, void* out,
                               const int* rows, int n_rows, int H, float eps, cudaStream_t stream) {
@@ -326,4 +436,14 @@ extern "C" int q3_rmsnorm(const void* x, const float* w, void* y, int dtype, int
   else
     return Q3_ERR_DTYPE;
   return q3::launch_status();
+}
+
+// resid[r, :] = rmsnorm(alpha * resid[r, :] + delta[r, :]) * w in place (delta may be null); out (may be
+// null) gets the same rows in `dtype`.  resid float32 [n_rows, H]; delta and out in `dtype`; w float32 [H].
+extern "C" int q3_scale_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, int dtype,
+                                    int n_rows, int H, float alpha, float eps, cudaStream_t stream) {
+  if (dtype == Q3_F32) return q3::scale_add_rmsnorm_launch<float>(resid, delta, w, out, n_rows, H, alpha, eps, stream);
+  if (dtype == Q3_BF16)
+    return q3::scale_add_rmsnorm_launch<__nv_bfloat16>(resid, delta, w, out, n_rows, H, alpha, eps, stream);
+  return Q3_ERR_DTYPE;
 }

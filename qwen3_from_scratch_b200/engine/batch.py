@@ -14,7 +14,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, cache_key
 from ..cache.storage import CacheStorage
 from ..parts.base import Runtime, StepContext
 
@@ -108,11 +108,12 @@ class BatchContext(StepContext):
             layout.append((name, width))
         return flat, layout
 
-    def pages(self, cache_id: int):
-        return self.storage.planes(cache_id), self._tables[self.storage.group_of(cache_id)]
+    def pages(self, cache_id: int, name: str = ""):
+        key = cache_key(cache_id, name)
+        return self.storage.planes(key), self._tables[self.storage.group_of(key)]
 
-    def state(self, cache_id: int):
-        return self.storage.states[cache_id]
+    def state(self, cache_id: int, name: str = ""):
+        return self.storage.states[cache_key(cache_id, name)]
 
     def build(self, entries: Sequence[Entry], vocab_size: int, table_stride: Optional[int] = None,
               keep_buffer: bool = False, ahead: int = 0) -> "BatchContext":

@@ -68,7 +68,7 @@ class Model:
         for call in self.spec.order:
             if call.cache is None:
                 continue
-            need = self.layers[call.layer].mixer.cache_spec()
+            need = self.layers[call.layer].cache_spec()
             if call.cache in needs:
                 if needs[call.cache] != need:
                     raise ValueError(f"cache {call.cache} is used by layers with different needs")

@@ -82,6 +82,26 @@ _SIGNATURES = {
                              _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "q3_sample": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ull, _c_int,
                   _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p],
+    "q3_scale_add_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float,
+                             _c_void_p],
+    "q3_gated_act": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_token_shift": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                       _c_int, _c_int, _c_void_p, _c_void_p],
+    "q3_causal_conv": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                       _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "q3_block_diag": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_rglru_scan": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                      _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                      _c_int, _c_void_p, _c_void_p],
+    "q3_selective_scan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                          _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_void_p, _c_void_p],
+    "q3_qk_gate_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+                        _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
+                        _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
+    "q3_attn_sigmoid": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                        _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                        _c_void_p, _c_void_p],
 }
 
 
@@ -260,6 +280,27 @@ def add_rmsnorm_rows(resid: torch.Tensor, delta: Optional[torch.Tensor], weight:
     _done("add_rmsnorm_rows", code, f"width {H}")
 
 
+def scale_add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                      out: Optional[torch.Tensor], alpha: float, eps: float) -> None:
+    """resid = rmsnorm(alpha * resid + delta) * weight, in place in the float32 stream; ``out`` (optional) gets
+    the same rows in its own dtype (the dtype of ``delta``)."""
+    _check("scale_add_rmsnorm.resid", resid, torch.float32)
+    _check("scale_add_rmsnorm.weight", weight, torch.float32)
+    T, H = resid.shape
+    dtype = None
+    for name, t in (("delta", delta), ("out", out)):
+        if t is not None:
+            _check(f"scale_add_rmsnorm.{name}", t, dtype)
+            dtype = t.dtype
+            if tuple(t.shape) != (T, H):
+                raise KernelError(f"scale_add_rmsnorm: {name} {tuple(t.shape)} vs stream {(T, H)}")
+    if weight.numel() != H:
+        raise KernelError(f"scale_add_rmsnorm: weight {tuple(weight.shape)}, stream {(T, H)}")
+    code = library().q3_scale_add_rmsnorm(resid.data_ptr(), _ptr(delta), weight.data_ptr(), _ptr(out),
+                                          dtype_tag(dtype or torch.float32), T, H, float(alpha), float(eps), _stream())
+    _done("scale_add_rmsnorm", code, f"width {H}")
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
     """out[r] = rmsnorm(x[r]) * weight over the last dimension."""
     _check("rmsnorm.x", x)
@@ -365,17 +406,31 @@ def attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out:
     _done("attn_ref", code, f"heads {Hq}/{Hkv}, head_dim {D}")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) -> None:
-    """out = up * silu(gate); gate = first half of the columns and up = second half, or with
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "none": 3}
+
+
+def activation_code(name: str, gate: bool = False) -> int:
+    if name not in ACTIVATIONS or (gate and name == "none"):
+        raise KernelError(f"activation '{name}' is not built (built: {', '.join(ACTIVATIONS)})")
+    return ACTIVATIONS[name]
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False, activation: str = "silu") -> None:
+    """out = up * act(gate); gate = first half of the columns and up = second half, or with
     ``interleave8`` alternating blocks of eight columns (gate, up, gate, up, ...)."""
-    _check("swiglu.gate_up", gate_up)
-    _check("swiglu.out", out, gate_up.dtype)
+    _check("gated_act.gate_up", gate_up)
+    _check("gated_act.out", out, gate_up.dtype)
     T, two_i = gate_up.shape
     if two_i % 2 or tuple(out.shape) != (T, two_i // 2):
-        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
-    code = library().q3_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T, two_i // 2,
-                               1 if interleave8 else 0, _stream())
-    _done("swiglu", code, f"width {two_i // 2}")
+        raise KernelError(f"gated_act: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+    code = library().q3_gated_act(gate_up.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T, two_i // 2,
+                                  1 if interleave8 else 0, activation_code(activation, gate=True), _stream())
+    _done("gated_act", code, f"width {two_i // 2}")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) -> None:
+    """``gated_act`` with the SiLU gate."""
+    gated_act(gate_up, out, interleave8, "silu")
 
 
 SKINNY_MAX_ROWS = 16  # rows of the few-rows product (two tiles of eight tokens)
@@ -846,3 +901,210 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
             attn_tc(q, k_pages, v_pages, out, *rest, scale, status)
         else:
             attn_prefill(q, k_pages, v_pages, out, *rest, scale, window, status)
+
+
+# ------------------------------------------------------------------ state carried from token to token
+def token_shift(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, tok_seq: torch.Tensor,
+                slot_ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t] = x[t] + (x[t - 1] - x[t]) * mu, the token before a portion's first one taken from ``state``
+    (float32 [slots, W], zero for a new request), which then receives the portion's last x."""
+    _check("token_shift.x", x, torch.float32)
+    _check("token_shift.mu", mu, torch.float32)
+    _check("token_shift.state", state, torch.float32)
+    _check("token_shift.out", out)
+    for name, t in (("q_start", q_start), ("tok_seq", tok_seq), ("slot_ids", slot_ids)):
+        _check(f"token_shift.{name}", t, torch.int32)
+    T, W = x.shape
+    if tuple(out.shape) != (T, W) or mu.numel() != W or state.dim() != 2 or state.shape[1] != W or tok_seq.numel() != T:
+        raise KernelError(f"token_shift: x {tuple(x.shape)}, out {tuple(out.shape)}, mu {tuple(mu.shape)}, "
+                          f"state {tuple(state.shape)}")
+    code = library().q3_token_shift(x.data_ptr(), mu.data_ptr(), state.data_ptr(), q_start.data_ptr(), tok_seq.data_ptr(),
+                                    slot_ids.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T, W, state.shape[0],
+                                    status.data_ptr(), _stream())
+    _done("token_shift", code)
+
+
+def causal_conv(x: torch.Tensor, column: int, in_bias: Optional[torch.Tensor], weight: torch.Tensor,
+                bias: Optional[torch.Tensor], state: torch.Tensor, q_start: torch.Tensor, tok_seq: torch.Tensor,
+                slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor, activation: str, status: torch.Tensor) -> None:
+    """A short causal convolution per channel over the columns ``column .. column + C`` of ``x`` [T, ld]:
+    out[t, c] = act(sum_j weight[c, j] * v[t - (K - 1 - j), c] + bias[c]), v = x + in_bias; what lies before a
+    portion comes from ``state`` (float32 [slots, K - 1, C], zero for a new request), which is renewed."""
+    _check("causal_conv.x", x)
+    _check("causal_conv.out", out, x.dtype)
+    _check("causal_conv.weight", weight, torch.float32)
+    _check("causal_conv.state", state, torch.float32)
+    for name, t in (("q_start", q_start), ("tok_seq", tok_seq), ("slot_ids", slot_ids)):
+        _check(f"causal_conv.{name}", t, torch.int32)
+    T, ld = x.shape
+    C, K = weight.shape
+    if (tuple(out.shape) != (T, C) or column < 0 or column + C > ld or state.dim() != 3
+            or tuple(state.shape[1:]) != (K - 1, C) or tok_seq.numel() != T or q_start.numel() < num_seqs + 1):
+        raise KernelError(f"causal_conv: x {tuple(x.shape)} column {column}, weight {tuple(weight.shape)}, out "
+                          f"{tuple(out.shape)}, state {tuple(state.shape)}")
+    for name, t in (("in_bias", in_bias), ("bias", bias)):
+        if t is not None:
+            _check(f"causal_conv.{name}", t, torch.float32)
+            if t.numel() != C:
+                raise KernelError(f"causal_conv: {name} has {t.numel()} values for {C} channels")
+    code = library().q3_causal_conv(x.data_ptr() + column * x.element_size(), ld, _ptr(in_bias), weight.data_ptr(),
+                                    _ptr(bias), state.data_ptr(), q_start.data_ptr(), tok_seq.data_ptr(),
+                                    slot_ids.data_ptr(), out.data_ptr(), dtype_tag(x.dtype), T, int(num_seqs), C, K,
+                                    activation_code(activation), state.shape[0], status.data_ptr(), _stream())
+    _done("causal_conv", code, f"channels {C}, taps {K}")
+
+
+BLOCK_DIAG_FEW_ROWS = 16  # up to so many tokens the engine's own kernel streams the weight once
+
+
+def block_diag(u: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b, t, r] = sum_e weight[b, r, e] * u[t, b * bw + e]: a block-diagonal product, float32 result
+    [blocks, T, rows].  u [T, blocks * bw] and weight [blocks, rows, bw] in one dtype.  bfloat16 with more than
+    ``BLOCK_DIAG_FEW_ROWS`` tokens: the library's batched product; otherwise the engine's own kernel."""
+    _check("block_diag.u", u)
+    _check("block_diag.weight", weight, u.dtype)
+    _check("block_diag.out", out, torch.float32)
+    T, C = u.shape
+    nb, rows, bw = weight.shape
+    if nb * bw != C or tuple(out.shape) != (nb, T, rows):
+        raise KernelError(f"block_diag: u {tuple(u.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if u.dtype == torch.bfloat16 and T > BLOCK_DIAG_FEW_ROWS:
+        torch.bmm(u.view(T, nb, bw).transpose(0, 1), weight.transpose(1, 2), out_dtype=torch.float32, out=out)
+        return
+    code = library().q3_block_diag(u.data_ptr(), weight.data_ptr(), out.data_ptr(), dtype_tag(u.dtype), T, nb, bw, rows,
+                                   _stream())
+    _done("block_diag", code, f"blocks {nb} of {bw}")
+
+
+def rglru_scan(proj: torch.Tensor, y_column: int, y_bias: Optional[torch.Tensor], u: torch.Tensor, gates: torch.Tensor,
+               ra_bias: torch.Tensor, ri_bias: torch.Tensor, lam: torch.Tensor, decay: float, state: torch.Tensor,
+               q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor,
+               status: torch.Tensor) -> None:
+    """The gated linear recurrence S = a S + sqrt(1 - a^2) (i * u) with a = exp(-decay * softplus(lam) * r),
+    r and i the sigmoids of ``gates`` (float32 [blocks, T, 2 bw]: per block the recurrence gate's rows, then the
+    input gate's) plus their biases; out = S * gelu_tanh(proj[:, y_column : y_column + C] + y_bias).  ``state``:
+    float32 [slots, C]."""
+    _check("rglru_scan.proj", proj)
+    _check("rglru_scan.u", u, proj.dtype)
+    _check("rglru_scan.out", out, proj.dtype)
+    _check("rglru_scan.gates", gates, torch.float32)
+    _check("rglru_scan.state", state, torch.float32)
+    T, C = u.shape
+    nb, Tg, two_bw = gates.shape
+    for name, t in (("ra_bias", ra_bias), ("ri_bias", ri_bias), ("lam", lam)) + ((("y_bias", y_bias),) if y_bias is not None else ()):
+        _check(f"rglru_scan.{name}", t, torch.float32)
+        if t.numel() != C:
+            raise KernelError(f"rglru_scan: {name} has {t.numel()} values for {C} channels")
+    if (Tg != T or nb * two_bw != 2 * C or tuple(out.shape) != (T, C) or proj.shape[0] != T or y_column < 0
+            or y_column + C > proj.shape[1] or state.dim() != 2 or state.shape[1] != C):
+        raise KernelError(f"rglru_scan: proj {tuple(proj.shape)}, u {tuple(u.shape)}, gates {tuple(gates.shape)}, "
+                          f"state {tuple(state.shape)}")
+    code = library().q3_rglru_scan(proj.data_ptr(), proj.shape[1], int(y_column), _ptr(y_bias), u.data_ptr(),
+                                   gates.data_ptr(), ra_bias.data_ptr(), ri_bias.data_ptr(), lam.data_ptr(), float(decay),
+                                   state.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(), out.data_ptr(),
+                                   dtype_tag(proj.dtype), T, int(num_seqs), C, two_bw // 2, state.shape[0],
+                                   status.data_ptr(), _stream())
+    _done("rglru_scan", code, f"channels {C}")
+
+
+def selective_scan(xc: torch.Tensor, proj: torch.Tensor, z_column: int, bc: torch.Tensor, dt: torch.Tensor,
+                   dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor,
+                   q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor,
+                   status: torch.Tensor) -> None:
+    """The selective scan: per channel c and state n, S = exp(step A[c, n]) S + step x B[n], y = sum_n S C[n] +
+    D x, out = y * silu(z); step = softplus(dt + dt_bias), A = -exp(a_log), z = proj[:, z_column : z_column + I];
+    bc: float32 [T, 2 N] (B then C); dt: float32 [T, I]; state: float32 [slots, N, I]."""
+    _check("selective_scan.xc", xc)
+    _check("selective_scan.proj", proj, xc.dtype)
+    _check("selective_scan.out", out, xc.dtype)
+    for name, t in (("bc", bc), ("dt", dt), ("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip), ("state", state)):
+        _check(f"selective_scan.{name}", t, torch.float32)
+    T, I = xc.shape
+    N = a_log.shape[1]
+    if (tuple(a_log.shape) != (I, N) or tuple(bc.shape) != (T, 2 * N) or tuple(dt.shape) != (T, I) or dt_bias.numel() != I
+            or d_skip.numel() != I or tuple(out.shape) != (T, I) or proj.shape[0] != T or z_column < 0
+            or z_column + I > proj.shape[1] or state.dim() != 3 or tuple(state.shape[1:]) != (N, I)):
+        raise KernelError(f"selective_scan: x {tuple(xc.shape)}, proj {tuple(proj.shape)}, bc {tuple(bc.shape)}, dt "
+                          f"{tuple(dt.shape)}, A {tuple(a_log.shape)}, state {tuple(state.shape)}")
+    code = library().q3_selective_scan(xc.data_ptr(), proj.data_ptr(), proj.shape[1], int(z_column), bc.data_ptr(),
+                                       dt.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(),
+                                       state.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(), out.data_ptr(),
+                                       dtype_tag(xc.dtype), T, int(num_seqs), I, N, state.shape[0], status.data_ptr(),
+                                       _stream())
+    _done("selective_scan", code, f"channels {I}, state {N}")
+
+
+# ------------------------------------------------------------------ attention without a softmax
+def qk_gate_post(proj: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                 q_weight: torch.Tensor, k_weight: torch.Tensor, eps: float, temp_coef: float, temp_every: int,
+                 positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, num_q_heads: int,
+                 num_kv_heads: int, head_dim: int, gate_out: Optional[torch.Tensor], write_kv: bool,
+                 status: torch.Tensor) -> None:
+    """From a step's projection [T, (Hq + Hkv) D (+ Hq)]: q normed per head, times the temperature
+    1 + coef * ln(floor((p + 1) / every) + 1) (``temp_every`` <= 0: none), to ``q_out``; k normed per head into
+    plane k of the pages and as projected into plane v; sigmoid of the last Hq columns to ``gate_out``."""
+    _check("qk_gate_post.proj", proj)
+    for name, t in (("q_out", q_out), ("k_pages", k_pages), ("v_pages", v_pages)):
+        _check(f"qk_gate_post.{name}", t, proj.dtype)
+    for name, t in (("positions", positions), ("tok_seq", tok_seq), ("block_table", block_table)):
+        _check(f"qk_gate_post.{name}", t, torch.int32)
+    for name, t in (("q_weight", q_weight), ("k_weight", k_weight)):
+        _check(f"qk_gate_post.{name}", t, torch.float32)
+        if t.numel() != head_dim:
+            raise KernelError(f"qk_gate_post: {name} has {t.numel()} values, the heads are {head_dim} wide")
+    T, ld = proj.shape
+    need = (num_q_heads + num_kv_heads) * head_dim + (num_q_heads if gate_out is not None else 0)
+    num_pages, hkv, page_size, d = k_pages.shape
+    if (ld != need or q_out.numel() != T * num_q_heads * head_dim or hkv != num_kv_heads or d != head_dim
+            or v_pages.shape != k_pages.shape or positions.numel() != T or tok_seq.numel() != T or block_table.dim() != 2):
+        raise KernelError(f"qk_gate_post: proj {tuple(proj.shape)} expected [T, {need}], q_out {tuple(q_out.shape)}, "
+                          f"pages {tuple(k_pages.shape)}")
+    if gate_out is not None:
+        _check("qk_gate_post.gate_out", gate_out, torch.float32)
+        if gate_out.numel() != T * num_q_heads:
+            raise KernelError(f"qk_gate_post: gate_out {tuple(gate_out.shape)} for {T} tokens of {num_q_heads} heads")
+    code = library().q3_qk_gate_post(proj.data_ptr(), dtype_tag(proj.dtype), T, ld, num_q_heads, num_kv_heads, head_dim,
+                                     q_weight.data_ptr(), k_weight.data_ptr(), float(eps), float(temp_coef),
+                                     int(temp_every), positions.data_ptr(), tok_seq.data_ptr(), block_table.data_ptr(),
+                                     block_table.shape[1], page_size, k_pages.data_ptr(), v_pages.data_ptr(), num_pages,
+                                     q_out.data_ptr(), _ptr(gate_out), 1 if write_kv else 0, status.data_ptr(), _stream())
+    _done("qk_gate_post", code, f"heads {num_q_heads}/{num_kv_heads} x {head_dim}")
+
+
+def attn_sigmoid(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                 head_bias: Optional[torch.Tensor], gate: Optional[torch.Tensor], q_start: torch.Tensor,
+                 kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, scale: float,
+                 status: torch.Tensor) -> None:
+    """Plain paged causal attention with sigmoid weights (one warp per query and head), any head size up to
+    512: out = gate * sum_n sigmoid(q . k_n * scale + head_bias[h]) v_n."""
+    _check("attn_sigmoid.q", q)
+    _check("attn_sigmoid.out", out, q.dtype)
+    _check("attn_sigmoid.k_pages", k_pages, q.dtype)
+    _check("attn_sigmoid.v_pages", v_pages, q.dtype)
+    for name, t in (("q_start", q_start), ("kv_len", kv_len), ("tok_seq", tok_seq), ("block_table", block_table)):
+        _check(f"attn_sigmoid.{name}", t, torch.int32)
+    T, Hq, D = q.shape
+    num_pages, Hkv, page_size, d = k_pages.shape
+    if d != D or v_pages.shape != k_pages.shape or out.numel() != q.numel() or block_table.dim() != 2:
+        raise KernelError(f"attn_sigmoid: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    for name, t, n in (("head_bias", head_bias, Hq), ("gate", gate, T * Hq)):
+        if t is not None:
+            _check(f"attn_sigmoid.{name}", t, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"attn_sigmoid: {name} has {t.numel()} values, {n} expected")
+    code = library().q3_attn_sigmoid(q.data_ptr(), dtype_tag(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
+                                     out.data_ptr(), _ptr(head_bias), _ptr(gate), q_start.data_ptr(), kv_len.data_ptr(),
+                                     tok_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
+                                     num_pages, T, Hq, Hkv, D, float(scale), status.data_ptr(), _stream())
+    _done("attn_sigmoid", code, f"heads {Hq}/{Hkv}, head_dim {D}")
+
+
+def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                      head_bias: Optional[torch.Tensor], gate: Optional[torch.Tensor], q_start: torch.Tensor,
+                      kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, num_seqs: int,
+                      num_decode: int, max_q_len: int, max_kv_len: int, scale: float, status: torch.Tensor) -> None:
+    """Causal attention with sigmoid weights of a mixed batch over the pages (see ``attn_sigmoid``)."""
+    if block_table.dim() != 2 or max_kv_len > block_table.shape[1] * k_pages.shape[2]:
+        raise KernelError(f"sigmoid_attention: the longest request has {max_kv_len} tokens, a block table row of "
+                          f"{block_table.shape[-1]} pages of {k_pages.shape[2]} holds fewer")
+    attn_sigmoid(q, k_pages, v_pages, out, head_bias, gate, q_start, kv_len, tok_seq, block_table, scale, status)

@@ -153,3 +153,71 @@ class GQAAttention(Mixer):
         ops.paged_attention(q, k_pages, v_pages, out, ctx.q_start, ctx.kv_len, ctx.tok_seq, table, ctx.num_seqs,
                             ctx.num_decode, ctx.max_q_len, ctx.max_kv_len, self.scale, self.window or 0,
                             self.rt.status, self._partial, raw_qkv=raw_qkv)
+
+
+@register_part("mixer", "sigmoid_attention")
+class SigmoidAttention(Mixer):
+    """Grouped-query causal attention whose weights are not normalised over the keys: a visible key n gets
+    sigmoid(q . k_n * scale + b_h), b_h one learned number per head, and the weighted values are summed as they
+    are.  The values are the keys as projected (there is no value projection): the cache holds the normed key in
+    plane ``k`` and the key before its norm in plane ``v``.  q and k are RMS-normed per head with one weight per
+    kind, shared by the heads; there is no rotation, positions enter through the causal mask and, optionally,
+    through a temperature on the query, tau(p) = 1 + coef * ln(floor((p + 1) / every) + 1).  Each head's output
+    is multiplied by sigmoid(W_g h)_h, a gate read from the mixer's input, before the output projection.
+    Scores, weights, norms, the temperature and the gate are float32 in every run.
+
+    One product gives q, k and the gates (``names``: the tensors' names after the part's own)."""
+
+    graph_capturable = True
+    NAMES = {"q": "q", "k": "k", "q_norm": "q.norm", "k_norm": "k.norm", "head_bias": "pb", "gate": "g", "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 qk_norm_eps: float, temp_coef: float = 0.0, temp_every: int = 0,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size = int(hidden_size)
+        self.num_heads, self.num_kv_heads, self.head_dim = int(num_heads), int(num_kv_heads), int(head_dim)
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"{self.num_heads} query heads are not a multiple of {self.num_kv_heads} kv heads")
+        self.scale, self.qk_norm_eps = float(scale), float(qk_norm_eps)
+        self.temp_coef, self.temp_every = float(temp_coef), int(temp_every)
+        n = dict(self.NAMES)
+        n.update(names or {})
+        self.tensors = {k: f"{name}.{v}" for k, v in n.items()}
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, h, d = self.tensors, self.hidden_size, self.head_dim
+        return [WeightSpec(t["q"], (self.num_heads * d, h)), WeightSpec(t["k"], (self.num_kv_heads * d, h)),
+                WeightSpec(t["q_norm"], (d,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["k_norm"], (d,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["head_bias"], (self.num_heads,), kind="vector", init="normal"),
+                WeightSpec(t["gate"], (self.num_heads, h)),
+                WeightSpec(t["out"], (h, self.num_heads * d))]
+
+    def cache_spec(self) -> KVCacheSpec:
+        return KVCacheSpec(self.num_kv_heads, self.head_dim)
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        t = self.tensors
+        q, k, g = weights.pop(t["q"]), weights.pop(t["k"]), weights.pop(t["gate"])
+        dtype = torch.float32 if torch.float32 in (q.dtype, k.dtype, g.dtype) else q.dtype
+        self.proj = Linear(torch.cat([q.to(dtype), k.to(dtype), g.to(dtype)], dim=0), rt, tag="sattn.proj")
+        del q, k, g
+        self.o_proj = Linear(weights.pop(t["out"]), rt, tag="sattn.o_proj")
+        self.q_norm_weight, self.k_norm_weight = weights[t["q_norm"]], weights[t["k_norm"]]
+        self.head_bias = weights[t["head_bias"]]
+        self._q = rt.shared("attn.q", rt.max_tokens, self.num_heads, self.head_dim)
+        self._o = rt.shared("attn.o", rt.max_tokens, self.num_heads, self.head_dim)
+        self._gate = rt.shared("sattn.gate", rt.max_tokens, self.num_heads, dtype=torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        T, hq, hkv, d = x.shape[0], self.num_heads, self.num_kv_heads, self.head_dim
+        k_pages, v_pages, table = ctx.kv(cache_id)
+        q, out, gate = self._q[:T], self._o[:T], self._gate[:T]
+        ops.qk_gate_post(self.proj(x), q, k_pages, v_pages, self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps,
+                         self.temp_coef, self.temp_every, ctx.positions, ctx.tok_seq, table, hq, hkv, d, gate, write_cache,
+                         self.rt.status)
+        ops.sigmoid_attention(q, k_pages, v_pages, out, self.head_bias, gate, ctx.q_start, ctx.kv_len, ctx.tok_seq, table,
+                              ctx.num_seqs, ctx.num_decode, ctx.max_q_len, ctx.max_kv_len, self.scale, self.rt.status)
+        return self.o_proj(out.view(T, hq * d))

@@ -155,7 +155,8 @@ class StepContext:
     (rows that bring exactly one token come first in the batch).
     ``pages(cache_id)`` gives ``({plane name: pages}, block_table)`` of a cache of pages,
     ``kv(cache_id)`` the same as ``(k_pages, v_pages, block_table)`` for a cache with planes ``k`` and
-    ``v``, and ``state(cache_id)`` the ``[slots, *shape]`` tensor of a cache of fixed-size state.
+    ``v``, and ``state(cache_id)`` the ``[slots, *shape]`` tensor of a cache of fixed-size state.  A part
+    whose ``cache_spec()`` names several needs asks for each by its name: ``state(cache_id, "conv")``.
     ``extra``: per-token integer arrays that the caller sent along with the tokens (``Entry.extra``),
     by name, int32 ``[T, width]`` on the device: positions on several axes, segment ids, whatever a part
     of the model defines for itself; ``positions`` (``start + i``) is always there.
@@ -185,16 +186,16 @@ class StepContext:
             store[key] = make()
         return store[key]
 
-    def pages(self, cache_id: int):  # pragma: no cover - interface
+    def pages(self, cache_id: int, name: str = ""):  # pragma: no cover - interface
         raise NotImplementedError
 
-    def kv(self, cache_id: int):
-        planes, table = self.pages(cache_id)
+    def kv(self, cache_id: int, name: str = ""):
+        planes, table = self.pages(cache_id, name)
         return planes["k"], planes["v"], table
 
     extra: Dict[str, torch.Tensor] = {}
 
-    def state(self, cache_id: int):  # pragma: no cover - interface
+    def state(self, cache_id: int, name: str = ""):  # pragma: no cover - interface
         raise NotImplementedError
 
 
@@ -289,9 +290,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_spec(self) -> CacheSpec:
+    def cache_spec(self) -> Union[CacheSpec, Dict[str, CacheSpec]]:
         """What the mixer keeps per request: ``PagedCacheSpec`` (``KVCacheSpec(...)`` for keys and values),
-        ``StateSpec``, or None."""
+        ``StateSpec``, or None; or several of these by name (``{"state": StateSpec(...), "conv": StateSpec(...)}``),
+        which it then asks the context for by that name."""
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
@@ -317,6 +319,11 @@ class Block(Part):
     #: a block that sets this leaves ``ctx.per_step[STREAM_SUMSQ]`` describing the stream as it returns it
     #: (and returns no pending output); after any other block the model drops the entry
     keeps_stream_stats = False
+
+    def cache_spec(self) -> Union[CacheSpec, Dict[str, CacheSpec]]:
+        """What one run of the block keeps per request: its mixer's needs, and for a block with state of its
+        own (the last input of a shift, ...) those as well, by name."""
+        return self.mixer.cache_spec()
 
     def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache_id: Optional[int], write_cache: bool) -> Optional[torch.Tensor]:

@@ -1,4 +1,7 @@
-"""Pre-norm residual block: h = x + mixer(norm1(x)); y = h + feed_forward(norm2(h)).
+"""The arrangements of norms, mixer and feed-forward around the residual stream: the norm before each
+sub-layer (``pre_norm``) and the norm after each sub-layer's sum (``post_norm``, at the end of the file).
+
+Pre-norm residual block: h = x + mixer(norm1(x)); y = h + feed_forward(norm2(h)).
 
 Reference: models/transformer_block.py:38-46.  The residual stream is float32 and the sums are
 fused into the norms: a block receives the previous sub-layer's output as ``pending`` and hands
@@ -14,7 +17,8 @@ from typing import Dict, List, Optional
 import torch
 
 from ..registry import create_part, register_part
-from .base import NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, Runtime, StepContext, WeightSpec
+from ..kernels import ops
+from .base import NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, Runtime, StateSpec, StepContext, WeightSpec
 
 
 @register_part("block", "pre_norm")
@@ -74,3 +78,89 @@ class PreNormBlock(Block):
         a = self.mixer.forward(x, ctx, cache_id, write_cache)
         x = self.norm2.add_norm(stream, a)
         return self.feed_forward.forward(x)
+
+
+@register_part("block", "post_norm")
+class PostNormBlock(Block):
+    """The norm after the sum: x <- norm1(alpha * x + mixer(h)); x <- norm2(alpha * x + feed_forward(x)).  The
+    sub-layers read the stream itself, which the norms keep normed.  With ``token_shift`` the mixer reads
+
+        h_t = x_t + (x_{t-1} - x_t) * mu        (mu: the tensor ``<name>.<shift>``, one value per feature)
+
+    instead of x_t, x_{-1} = 0; the last x of a request is kept in a state slot of the block's own (``shift``
+    in its cache needs) beside whatever the mixer keeps.  ``feed_forward`` may be None: the block is then the
+    mixer and its norm alone.  The stream stays float32; the operands of the projections are the compute dtype.
+    """
+
+    def __init__(self, name: str, norm1: PartSpec, mixer: PartSpec, norm2: Optional[PartSpec] = None,
+                 feed_forward: Optional[PartSpec] = None, alpha: float = 1.0, token_shift: bool = False,
+                 width: int = 0, names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        n = {"norm1": "norm1", "mixer": "mixer", "norm2": "norm2", "feed_forward": "feed_forward", "shift": "shift"}
+        n.update(names or {})
+        self.alpha = float(alpha)
+        self.norm1 = create_part("norm", norm1, name=f"{name}.{n['norm1']}")
+        self.mixer = create_part("mixer", mixer, name=f"{name}.{n['mixer']}")
+        self.feed_forward = self.norm2 = None
+        if feed_forward is not None:
+            if norm2 is None:
+                raise ValueError(f"block {name}: a feed-forward needs the norm that follows it")
+            self.norm2 = create_part("norm", norm2, name=f"{name}.{n['norm2']}")
+            self.feed_forward = create_part("feed_forward", feed_forward, name=f"{name}.{n['feed_forward']}")
+        self.token_shift = bool(token_shift)
+        self.shift_tensor = f"{name}.{n['shift']}"
+        self.width = int(width)
+        if self.width <= 0:
+            raise ValueError(f"block {name}: needs the stream's width")
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    @property
+    def graph_capturable(self) -> bool:
+        return all(p.graph_capturable for p in self._parts())
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [s for p in self._parts() for s in p.weight_specs()]
+        if self.token_shift:
+            specs.append(WeightSpec(self.shift_tensor, (self.width,), kind="vector", init="normal"))
+        return specs
+
+    def cache_spec(self):
+        need = self.mixer.cache_spec()
+        if not self.token_shift:
+            return need
+        needs = dict(need) if isinstance(need, dict) else {"": need}
+        if "shift" in needs:
+            raise ValueError(f"block {self.name}: its mixer already keeps something called 'shift'")
+        needs["shift"] = StateSpec((self.width,), "float32")
+        return needs
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        for part in self._parts():
+            part.setup(rt, weights)
+        if self.token_shift:
+            self.mu = weights[self.shift_tensor]
+        self._shifted = rt.shared("block.shifted", rt.max_tokens, self.width)
+
+    def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache_id: Optional[int], write_cache: bool) -> Optional[torch.Tensor]:
+        if pending is not None:  # a block before this one left a sum open: close it without a norm
+            stream.add_(pending.to(stream.dtype))
+        T = stream.shape[0]
+        if self.token_shift:
+            h = self._shifted[:T]
+            ops.token_shift(stream, self.mu, ctx.state(cache_id, "shift"), ctx.q_start, ctx.tok_seq, ctx.slot_ids, h,
+                            self.rt.status)
+        elif self.rt.dtype == torch.float32:
+            h = stream
+        else:
+            h = self._shifted[:T]
+            h.copy_(stream)
+        a = self.mixer.forward(h, ctx, cache_id, write_cache)
+        x = self.norm1.scale_add_norm(stream, a, self.alpha, want_copy=self.feed_forward is not None)
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(x)
+            self.norm2.scale_add_norm(stream, f, self.alpha, want_copy=False)
+        return None

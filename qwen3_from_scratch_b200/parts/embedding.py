@@ -21,16 +21,18 @@ from .linear import Linear
 class TokenEmbedding(Part):
     graph_capturable = True
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int):
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, suffix: str = ".weight"):
+        """``suffix``: what follows the part's name in its tensor's name ("" for a tensor named like the part)."""
         super().__init__(name)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.tensor = f"{name}{suffix}"
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(f"{self.name}.weight", (self.vocab_size, self.hidden_size))]
+        return [WeightSpec(self.tensor, (self.vocab_size, self.hidden_size))]
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
-        self.weight = weights[f"{self.name}.weight"]
+        self.weight = weights[self.tensor]
         self._stream = rt.shared("stream", rt.max_tokens, self.hidden_size, dtype=torch.float32)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
@@ -45,19 +47,21 @@ class LMHead(Part):
 
     """logits = x W^T in float32.  ``tied_to``: name of the embedding tensor it shares, or None."""
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None,
+                 suffix: str = ".weight"):
         super().__init__(name)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.tied_to = tied_to
+        self.tensor = f"{name}{suffix}"
 
     def weight_specs(self) -> List[WeightSpec]:
         if self.tied_to:
             return []
-        return [WeightSpec(f"{self.name}.weight", (self.vocab_size, self.hidden_size))]
+        return [WeightSpec(self.tensor, (self.vocab_size, self.hidden_size))]
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
-        weight = weights[self.tied_to] if self.tied_to else weights[f"{self.name}.weight"]
+        weight = weights[self.tied_to] if self.tied_to else weights[self.tensor]
         self.proj = Linear(weight, rt, out_dtype=torch.float32, reuse_output=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -1,12 +1,14 @@
-"""SwiGLU feed-forward: y = (up(x) * silu(gate(x))) W_down^T, no biases.
+"""Gated feed-forward: y = (up(x) * act(gate(x))) W_down^T, no biases.  ``swiglu`` is the form with the SiLU
+gate and the checkpoint's ``gate_proj`` / ``up_proj`` / ``down_proj`` names; ``gated_mlp`` takes the gate's
+activation (``silu``, ``relu``, ``gelu_tanh``) and the tensors' names as parameters.
 
-Reference: models/feedback.py:14-34.  gate_proj and up_proj are merged into one
-[2I, H] weight at load (gate rows first), so one product feeds the gate kernel.
+Reference: models/feedback.py:14-34.  The gate and up weights are merged into one [2I, H] weight at load, so
+one product feeds the gate kernel.
 """
 
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -15,25 +17,34 @@ from ..registry import register_part
 from .base import FeedForward, Runtime, StreamNorm, WeightSpec
 from .linear import Linear
 
+_DEFAULT_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
 
-@register_part("feed_forward", "swiglu")
-class SwiGLU(FeedForward):
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(FeedForward):
     graph_capturable = True
 
-    def __init__(self, name: str, hidden_size: int, intermediate_size: int):
+    def __init__(self, name: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: Optional[Dict[str, str]] = None):
+        """``names``: what follows the part's name (and a dot) in the names of its gate, up and down tensors."""
         super().__init__(name)
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        ops.activation_code(activation, gate=True)
+        self.activation = activation
+        n = dict(_DEFAULT_NAMES)
+        n.update(names or {})
+        self.tensors = {k: f"{name}.{v}" for k, v in n.items()}
 
     def weight_specs(self) -> List[WeightSpec]:
         h, i = self.hidden_size, self.intermediate_size
-        return [WeightSpec(f"{self.name}.gate_proj.weight", (i, h)),
-                WeightSpec(f"{self.name}.up_proj.weight", (i, h)),
-                WeightSpec(f"{self.name}.down_proj.weight", (h, i))]
+        return [WeightSpec(self.tensors["gate"], (i, h)),
+                WeightSpec(self.tensors["up"], (i, h)),
+                WeightSpec(self.tensors["down"], (h, i))]
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
-        gate = weights.pop(f"{self.name}.gate_proj.weight")
-        up = weights.pop(f"{self.name}.up_proj.weight")
+        gate = weights.pop(self.tensors["gate"])
+        up = weights.pop(self.tensors["up"])
         dtype = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
         h, i = self.hidden_size, self.intermediate_size
         # bfloat16: gate and up rows alternate in blocks of eight, so that the decode kernel has a
@@ -45,13 +56,15 @@ class SwiGLU(FeedForward):
             merged = torch.cat([gate.to(dtype), up.to(dtype)], dim=0)
         del gate, up
         self.gate_up = Linear(merged, rt, tag="ffn.gate_up")
-        self.down = Linear(weights.pop(f"{self.name}.down_proj.weight"), rt, tag="ffn.down")
+        self.down = Linear(weights.pop(self.tensors["down"]), rt, tag="ffn.down")
         self._act = rt.shared("ffn.act", rt.max_tokens, self.intermediate_size)
+        # the products that apply the gate in their epilogue are built for the SiLU gate
+        self.fused_gate = self.blocks_of_eight and self.activation == "silu"
 
     fuses_stream = True
 
     def can_fuse_stream(self, rows: int) -> bool:
-        return self.blocks_of_eight and self.gate_up.takes_stream_norm(rows) and self.down.can_add_into_stream(rows)
+        return self.fused_gate and self.gate_up.takes_stream_norm(rows) and self.down.can_add_into_stream(rows)
 
     def forward(self, x, into_stream=None, next_norm_weight=None):
         act = self._act[: x.shape[0]]
@@ -59,17 +72,23 @@ class SwiGLU(FeedForward):
         if isinstance(x, StreamNorm):
             # decoding without norm kernels: the norm is applied inside the gate/up product
             ops.gemm_skinny_normed(x.scaled, x.sumsq, x.parts, x.eps, self.gate_up.weight, act, swiglu_blocks=True)
-        elif self.blocks_of_eight and ops.gemm_skinny_takes(rows, self.gate_up.weight):
+        elif self.fused_gate and ops.gemm_skinny_takes(rows, self.gate_up.weight):
             # decoding: stream the weight once, activation applied before the store
             ops.gemm_skinny(x, self.gate_up.weight, act, swiglu_blocks=True)
-        elif (self.blocks_of_eight and ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight)
+        elif (self.fused_gate and ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight)
               and ops.gemm_tc_takes(x, self.gate_up.weight)):
             # prompt portions: the engine's tcgen05 product with the activation in its epilogue, so the
             # [T, 2I] gate/up product never goes to memory
             ops.gemm_tc(x, self.gate_up.weight, act, self.rt.status, swiglu_blocks=True,
                         pair=ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight) == "pair")
         else:
-            ops.swiglu(self.gate_up(x), act, interleave8=self.blocks_of_eight)
+            ops.gated_act(self.gate_up(x), act, interleave8=self.blocks_of_eight, activation=self.activation)
         if into_stream is not None:
             return self.down.into_stream(act, into_stream, next_norm_weight)
         return self.down(act)
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(GatedMLP):
+    def __init__(self, name: str, hidden_size: int, intermediate_size: int):
+        super().__init__(name, hidden_size, intermediate_size, activation="silu")

@@ -19,16 +19,19 @@ from .base import Norm, Runtime, StreamNorm, StreamStats, WeightSpec
 class RMSNorm(Norm):
     graph_capturable = True
 
-    def __init__(self, name: str, dim: int, eps: float):
+    def __init__(self, name: str, dim: int, eps: float, suffix: str = ".weight"):
+        """``suffix``: what follows the part's name in its tensor's name ("" where the tensor bears the
+        part's name itself)."""
         super().__init__(name)
         self.dim, self.eps = int(dim), float(eps)
+        self.tensor = f"{name}{suffix}"
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(f"{self.name}.weight", (self.dim,), kind="vector", init="one_plus_normal")]
+        return [WeightSpec(self.tensor, (self.dim,), kind="vector", init="one_plus_normal")]
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
-        self.weight = weights[f"{self.name}.weight"]
+        self.weight = weights[self.tensor]
         self._out = rt.shared("normed", rt.max_tokens, self.dim)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -39,6 +42,17 @@ class RMSNorm(Norm):
     def add_norm(self, stream: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         out = self._out[: stream.shape[0]]
         ops.add_rmsnorm(stream, delta, self.weight, out, self.eps)
+        return out
+
+    def scale_add_norm(self, stream: torch.Tensor, delta: Optional[torch.Tensor], alpha: float,
+                       want_copy: bool = True) -> Optional[torch.Tensor]:
+        """The norm after the sum: stream = norm(alpha * stream + delta) in place; returns the new rows in the
+        compute dtype for the next projection (``want_copy``; in a float32 run the stream itself)."""
+        if self.rt.dtype == torch.float32 or not want_copy:
+            ops.scale_add_rmsnorm(stream, delta, self.weight, None, alpha, self.eps)
+            return stream if want_copy else None
+        out = self._out[: stream.shape[0]]
+        ops.scale_add_rmsnorm(stream, delta, self.weight, out, alpha, self.eps)
         return out
 
     def lazy(self, stream: torch.Tensor, stats: StreamStats) -> Optional[StreamNorm]:

@@ -1,0 +1,163 @@
+"""Mixers that carry a state of fixed size from token to token instead of a cache of keys.
+
+``rglru``           the recurrent block of Griffin (De et al., "Griffin: Mixing Gated Linear Recurrences with
+                    Local Attention for Efficient Language Models"): two branches of ``width`` channels,
+                    y = gelu_tanh(W_y h + b_y) and u = conv(W_x h + b_x); block-diagonal gates
+                    r = sigmoid(R_b u_b + b), i = sigmoid(I_b u_b + b); a = exp(-decay * softplus(lam) * r);
+                    S_t = a S_{t-1} + sqrt(1 - a^2) (i * u); out = W_o (S * y).
+``selective_scan``  the mixer of Mamba (Gu and Dao, "Mamba: Linear-Time Sequence Modeling with Selective State
+                    Spaces"): [x | z] = W_in h; x = silu(conv(x)); [dt | B | C] = W_x x;
+                    step = softplus(W_dt dt + b); S[c, n] = exp(step_c A[c, n]) S[c, n] + step_c x_c B_n;
+                    y_c = sum_n S[c, n] C_n + D_c x_c; out = W_o (y * silu(z)).
+
+Both keep two things per request, named in ``cache_spec()``: ``state`` (float32) and ``conv`` (the last
+taps - 1 inputs of the short convolution, float32).  A new request's slot is zero.  The projections are
+``Linear``s (the compute dtype, float32 accumulation); decays, step sizes, gates and the state are float32 in
+every run; a portion of a prompt is walked token by token in the same order as the whole prompt.
+The names of the tensors are parameters (``names``), with the defaults below.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops
+from ..registry import register_part
+from .base import Mixer, Runtime, StateSpec, StepContext, WeightSpec
+from .linear import Linear
+
+
+class _NamedTensors:
+    def _name_tensors(self, name: str, defaults: Dict[str, str], names: Optional[Dict[str, str]]) -> None:
+        n = dict(defaults)
+        n.update(names or {})
+        self.tensors = {k: f"{name}.{v}" for k, v in n.items()}
+
+
+@register_part("mixer", "rglru")
+class RGLRU(Mixer, _NamedTensors):
+    graph_capturable = True
+    NAMES = {"y": "y", "y_bias": "y.b", "x": "x", "x_bias": "x.b", "conv": "conv", "conv_bias": "conv.b",
+             "gate_a": "ra", "gate_a_bias": "ra.b", "gate_i": "ri", "gate_i_bias": "ri.b", "lam": "lam", "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, width: int, blocks: int, conv: int, decay: float = 8.0,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.width, self.blocks, self.taps = int(hidden_size), int(width), int(blocks), int(conv)
+        if self.width % self.blocks:
+            raise ValueError(f"{self.width} channels are not a multiple of {self.blocks} blocks")
+        self.block_width = self.width // self.blocks
+        self.decay = float(decay)
+        self._name_tensors(name, self.NAMES, names)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, h, c, nb, bw = self.tensors, self.hidden_size, self.width, self.blocks, self.block_width
+        return [WeightSpec(t["y"], (c, h)), WeightSpec(t["y_bias"], (c,), kind="vector", init="normal"),
+                WeightSpec(t["x"], (c, h)), WeightSpec(t["x_bias"], (c,), kind="vector", init="normal"),
+                WeightSpec(t["conv"], (c, self.taps), kind="vector", init="normal"),
+                WeightSpec(t["conv_bias"], (c,), kind="vector", init="normal"),
+                WeightSpec(t["gate_a"], (nb, bw, bw)), WeightSpec(t["gate_a_bias"], (nb, bw), kind="vector", init="normal"),
+                WeightSpec(t["gate_i"], (nb, bw, bw)), WeightSpec(t["gate_i_bias"], (nb, bw), kind="vector", init="normal"),
+                WeightSpec(t["lam"], (c,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["out"], (h, c))]
+
+    def cache_spec(self):
+        return {"state": StateSpec((self.width,), "float32"),
+                "conv": StateSpec((self.taps - 1, self.width), "float32")}
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        t, c = self.tensors, self.width
+        y, x = weights.pop(t["y"]), weights.pop(t["x"])
+        dtype = torch.float32 if torch.float32 in (y.dtype, x.dtype) else y.dtype
+        self.proj = Linear(torch.cat([y.to(dtype), x.to(dtype)], dim=0), rt, tag="rglru.proj")  # columns: y, then x
+        del y, x
+        self.y_bias, self.x_bias = weights[t["y_bias"]], weights[t["x_bias"]]
+        self.conv_weight, self.conv_bias = weights[t["conv"]], weights[t["conv_bias"]]
+        ga, gi = weights.pop(t["gate_a"]), weights.pop(t["gate_i"])
+        # per block the rows of the recurrence gate, then those of the input gate: one product gives both
+        self.gate_weight = torch.cat([ga, gi], dim=1).to(rt.dtype).contiguous()
+        del ga, gi
+        self.gate_a_bias = weights[t["gate_a_bias"]].reshape(-1).contiguous()
+        self.gate_i_bias = weights[t["gate_i_bias"]].reshape(-1).contiguous()
+        self.lam = weights[t["lam"]]
+        self.out_proj = Linear(weights.pop(t["out"]), rt, tag="rglru.out")
+        self._u = rt.shared("rglru.u", rt.max_tokens, c)
+        self._gates = rt.shared("rglru.gates", rt.max_tokens * 2 * c, dtype=torch.float32)
+        self._gated = rt.shared("rglru.gated", rt.max_tokens, c)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        T, c, bw = x.shape[0], self.width, self.block_width
+        status = self.rt.status
+        proj = self.proj(x)
+        u = self._u[:T]
+        ops.causal_conv(proj, c, self.x_bias, self.conv_weight, self.conv_bias, ctx.state(cache_id, "conv"), ctx.q_start,
+                        ctx.tok_seq, ctx.slot_ids, ctx.num_seqs, u, "none", status)
+        gates = self._gates[: T * 2 * c].view(self.blocks, T, 2 * bw)
+        ops.block_diag(u, self.gate_weight, gates)
+        gated = self._gated[:T]
+        ops.rglru_scan(proj, 0, self.y_bias, u, gates, self.gate_a_bias, self.gate_i_bias, self.lam, self.decay,
+                       ctx.state(cache_id, "state"), ctx.q_start, ctx.slot_ids, ctx.num_seqs, gated, status)
+        return self.out_proj(gated)
+
+
+@register_part("mixer", "selective_scan")
+class SelectiveScan(Mixer, _NamedTensors):
+    graph_capturable = True
+    NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "x": "x", "dt": "dt", "dt_bias": "dt.b",
+             "a_log": "A_log", "d": "D", "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, inner: int, state: int, dt_rank: int, conv: int,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.inner, self.state_size = int(hidden_size), int(inner), int(state)
+        self.dt_rank, self.taps = int(dt_rank), int(conv)
+        self._name_tensors(name, self.NAMES, names)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, h, i, n, r = self.tensors, self.hidden_size, self.inner, self.state_size, self.dt_rank
+        return [WeightSpec(t["in"], (2 * i, h)),
+                WeightSpec(t["conv"], (i, self.taps), kind="vector", init="normal"),
+                WeightSpec(t["conv_bias"], (i,), kind="vector", init="normal"),
+                WeightSpec(t["x"], (r + 2 * n, i)),
+                WeightSpec(t["dt"], (i, r)), WeightSpec(t["dt_bias"], (i,), kind="vector", init="normal"),
+                WeightSpec(t["a_log"], (i, n), kind="vector", init="normal"),
+                WeightSpec(t["d"], (i,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["out"], (h, i))]
+
+    def cache_spec(self):
+        return {"state": StateSpec((self.state_size, self.inner), "float32"),
+                "conv": StateSpec((self.taps - 1, self.inner), "float32")}
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        t, i, n, r = self.tensors, self.inner, self.state_size, self.dt_rank
+        self.in_proj = Linear(weights.pop(t["in"]), rt, tag="scan.in")  # columns: x, then z
+        self.conv_weight, self.conv_bias = weights[t["conv"]], weights[t["conv_bias"]]
+        wx = weights.pop(t["x"])
+        # the low-rank step sizes feed another product, so they come out in the compute dtype; B and C enter the
+        # recurrence and come out in float32
+        self.dt_low = Linear(wx[:r].contiguous(), rt, tag="scan.dt_low")
+        self.bc_proj = Linear(wx[r:].contiguous(), rt, tag="scan.bc", out_dtype=torch.float32)
+        del wx
+        self.dt_proj = Linear(weights.pop(t["dt"]), rt, tag="scan.dt", out_dtype=torch.float32)
+        self.dt_bias, self.a_log, self.d_skip = weights[t["dt_bias"]], weights[t["a_log"]], weights[t["d"]]
+        self.out_proj = Linear(weights.pop(t["out"]), rt, tag="scan.out")
+        self._xc = rt.shared("scan.xc", rt.max_tokens, i)
+        self._y = rt.shared("scan.y", rt.max_tokens, i)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        T, i = x.shape[0], self.inner
+        status = self.rt.status
+        proj = self.in_proj(x)
+        xc = self._xc[:T]
+        ops.causal_conv(proj, 0, None, self.conv_weight, self.conv_bias, ctx.state(cache_id, "conv"), ctx.q_start,
+                        ctx.tok_seq, ctx.slot_ids, ctx.num_seqs, xc, "silu", status)
+        bc = self.bc_proj(xc)
+        dt = self.dt_proj(self.dt_low(xc))
+        y = self._y[:T]
+        ops.selective_scan(xc, proj, i, bc, dt, self.dt_bias, self.a_log, self.d_skip, ctx.state(cache_id, "state"),
+                           ctx.q_start, ctx.slot_ids, ctx.num_seqs, y, status)
+        return self.out_proj(y)

@@ -75,19 +75,21 @@ def _entry(name: str):
 
 def load_config(folder_or_file: str) -> ModelConfig:
     """Reads config.json and returns the typed configuration of the architecture it names."""
-    data = read_config_json(folder_or_file)
+    return config_from_dict(read_config_json(folder_or_file))
+
+
+def architecture_name(data: dict) -> str:
+    """The name a config.json chooses its model class by: ``architectures[0]``, or a single ``architecture``."""
     archs = data.get("architectures")
-    if not isinstance(archs, (list, tuple)) or not archs:
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
-    config_cls, _ = _entry(archs[0])
-    return config_cls.from_dict(data)
+    if isinstance(archs, (list, tuple)) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if archs is None and isinstance(data.get("architecture"), str):
+        return data["architecture"]
+    raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
 
 
 def config_from_dict(data: dict) -> ModelConfig:
-    archs = data.get("architectures")
-    if not isinstance(archs, (list, tuple)) or not archs:
-        raise ConfigError("config: 'architectures' must be a non-empty list of names")
-    config_cls, _ = _entry(archs[0])
+    config_cls, _ = _entry(architecture_name(data))
     return config_cls.from_dict(data)
 
 
@@ -103,5 +105,5 @@ def _load_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from .parts import attention, block, embedding, mlp, norm, rope  # noqa: F401  register themselves
-        from .models import qwen3  # noqa: F401  registers the architecture
+        from .parts import attention, block, embedding, mlp, norm, recurrent, rope  # noqa: F401  register themselves
+        from .models import binupel, qwen3  # noqa: F401  register the architectures
