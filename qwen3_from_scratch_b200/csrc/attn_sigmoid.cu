@@ -93,13 +93,13 @@ attn_sigmoid_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, cons
     for (int e = lane; e < D; e += 32) o[e] = from_float<T>(0.f);
     return;
   }
-  float qv[NJ], acc[NJ];
+  float qv[NJ], acc[NJ], comp[NJ];
   const T* qp = q + ((size_t)t * Hq + head) * D;
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
     const int e = lane + 32 * j;
     qv[j] = e < D ? to_float(qp[e]) : 0.f;
-    acc[j] = 0.f;
+    acc[j] = comp[j] = 0.f;
   }
   const float hb = head_bias ? head_bias[head] : 0.f;
   const int* table = block_table + (size_t)b * table_stride;
@@ -123,7 +123,16 @@ attn_sigmoid_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, cons
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
       const int e = lane + 32 * j;
-      if (e < D) acc[j] = fmaf(p, to_float(vp[e]), acc[j]);
+      if (e >= D) continue;
+      if (sizeof(T) == 4) {
+        // float32 run: compensated summation, so that a sum over thousands of keys stays at float32's own rounding
+        const float y = fmaf(p, to_float(vp[e]), -comp[j]);
+        const float tot = acc[j] + y;
+        comp[j] = (tot - acc[j]) - y;
+        acc[j] = tot;
+      } else {
+        acc[j] = fmaf(p, to_float(vp[e]), acc[j]);
+      }
     }
   }
   const float g = gate ? gate[(size_t)t * Hq + head] : 1.f;

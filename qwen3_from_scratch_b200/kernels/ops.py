@@ -99,6 +99,9 @@ _SIGNATURES = {
     "q3_qk_gate_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                         _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
+    "q3_attn_sigmoid_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                            _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                            _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
     "q3_attn_sigmoid": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                         _c_void_p, _c_void_p],
@@ -1099,12 +1102,79 @@ def attn_sigmoid(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
     _done("attn_sigmoid", code, f"heads {Hq}/{Hkv}, head_dim {D}")
 
 
+SIGMOID_MAX_SPLITS = 32
+
+
+def sigmoid_attention_fast(dtype: torch.dtype, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Whether the tensor-core kernel takes the shape (else the plain one runs)."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and num_q_heads % num_kv_heads == 0
+
+
+def sigmoid_partial_numel(num_seqs: int, num_q_heads: int, head_dim: int) -> int:
+    return num_seqs * SIGMOID_MAX_SPLITS * num_q_heads * head_dim
+
+
+def sigmoid_decode_splits(num_seqs: int, num_kv_heads: int, max_kv_len: int) -> int:
+    """Key ranges per sequence of the decode form: enough blocks for two per SM, but no range under four
+    tiles of 64 keys."""
+    tiles = max(1, -(-max_kv_len // 64))
+    want = -(-2 * sm_count() // max(1, num_seqs * num_kv_heads))
+    return max(1, min(SIGMOID_MAX_SPLITS, tiles // 4, want))
+
+
+def attn_sigmoid_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                     head_bias: Optional[torch.Tensor], gate: Optional[torch.Tensor], q_start: torch.Tensor,
+                     kv_len: torch.Tensor, block_table: torch.Tensor, num_seqs: int, max_q_len: int, scale: float,
+                     status: torch.Tensor, decode: bool = False, num_splits: int = 1,
+                     partial: Optional[torch.Tensor] = None) -> None:
+    """The tensor-core kernel for ``num_seqs`` rows of the batch (q_start has num_seqs + 1 entries): portions of
+    any length, or with ``decode`` one token per row, the keys cut into ``num_splits`` ranges."""
+    T, Hq, D, num_pages, Hkv, page_size = _attn_common("attn_sigmoid_mma", q, k_pages, v_pages, out, q_start, kv_len,
+                                                        block_table)
+    if q_start.numel() < num_seqs + (0 if decode else 1) or kv_len.numel() < num_seqs or block_table.shape[0] < num_seqs:
+        raise KernelError(f"attn_sigmoid_mma: {num_seqs} sequences, q_start {q_start.numel()}, kv_len {kv_len.numel()}")
+    for name, t, n in (("head_bias", head_bias, Hq), ("gate", gate, T * Hq)):
+        if t is not None:
+            _check(f"attn_sigmoid_mma.{name}", t, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"attn_sigmoid_mma: {name} has {t.numel()} values, {n} expected")
+    if decode and num_splits > 1:
+        if partial is None:
+            raise KernelError("attn_sigmoid_mma: more than one key range needs scratch memory")
+        _check("attn_sigmoid_mma.partial", partial, torch.float32)
+        if partial.numel() < num_seqs * num_splits * Hq * D:
+            raise KernelError(f"attn_sigmoid_mma: scratch of {partial.numel()} floats for {num_seqs} x {num_splits} ranges")
+    code = library().q3_attn_sigmoid_mma(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                         _ptr(partial), _ptr(head_bias), _ptr(gate), q_start.data_ptr(), kv_len.data_ptr(),
+                                         block_table.data_ptr(), block_table.shape[1], page_size, num_pages, num_seqs,
+                                         int(max_q_len), Hq, Hkv, D, float(scale), 1 if decode else 0, int(num_splits),
+                                         status.data_ptr(), _stream())
+    _done("attn_sigmoid_mma", code, f"heads {Hq}/{Hkv}, head_dim {D}")
+
+
 def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                       head_bias: Optional[torch.Tensor], gate: Optional[torch.Tensor], q_start: torch.Tensor,
                       kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, num_seqs: int,
-                      num_decode: int, max_q_len: int, max_kv_len: int, scale: float, status: torch.Tensor) -> None:
-    """Causal attention with sigmoid weights of a mixed batch over the pages (see ``attn_sigmoid``)."""
+                      num_decode: int, max_q_len: int, max_kv_len: int, scale: float, status: torch.Tensor,
+                      partial: Optional[torch.Tensor] = None, kernel: str = "auto") -> None:
+    """Causal attention with sigmoid weights of a mixed batch over the pages (see ``attn_sigmoid``): rows
+    [0, num_decode) bring one token each and go to the decode form of the tensor-core kernel, the rest to its
+    portion form; float32, shapes it refuses and ``kernel="plain"`` go to the plain kernel."""
+    T, Hq, D = q.shape
+    Hkv = k_pages.shape[1]
     if block_table.dim() != 2 or max_kv_len > block_table.shape[1] * k_pages.shape[2]:
         raise KernelError(f"sigmoid_attention: the longest request has {max_kv_len} tokens, a block table row of "
                           f"{block_table.shape[-1]} pages of {k_pages.shape[2]} holds fewer")
-    attn_sigmoid(q, k_pages, v_pages, out, head_bias, gate, q_start, kv_len, tok_seq, block_table, scale, status)
+    if kernel == "plain" or not sigmoid_attention_fast(q.dtype, Hq, Hkv, D):
+        attn_sigmoid(q, k_pages, v_pages, out, head_bias, gate, q_start, kv_len, tok_seq, block_table, scale, status)
+        return
+    decode = num_decode if Hq // Hkv <= 16 else 0  # a wider group's single tokens run as portions of one
+    if decode > 0:
+        splits = sigmoid_decode_splits(decode, Hkv, max_kv_len)
+        if partial is None or partial.numel() < decode * splits * Hq * D:
+            splits = 1 if partial is None else max(1, partial.numel() // (decode * Hq * D))
+        attn_sigmoid_mma(q, k_pages, v_pages, out, head_bias, gate, q_start, kv_len, block_table, decode, 1, scale,
+                         status, decode=True, num_splits=splits, partial=partial)
+    if num_seqs > decode:
+        attn_sigmoid_mma(q, k_pages, v_pages, out, head_bias, gate, q_start[decode:], kv_len[decode:],
+                         block_table[decode:], num_seqs - decode, max_q_len, scale, status)

@@ -210,6 +210,10 @@ class SigmoidAttention(Mixer):
         self._q = rt.shared("attn.q", rt.max_tokens, self.num_heads, self.head_dim)
         self._o = rt.shared("attn.o", rt.max_tokens, self.num_heads, self.head_dim)
         self._gate = rt.shared("sattn.gate", rt.max_tokens, self.num_heads, dtype=torch.float32)
+        self._partial = None
+        if ops.sigmoid_attention_fast(rt.dtype, self.num_heads, self.num_kv_heads, self.head_dim):
+            self._partial = rt.shared("sattn.partial", ops.sigmoid_partial_numel(rt.max_seqs, self.num_heads,
+                                                                                  self.head_dim), dtype=torch.float32)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         T, hq, hkv, d = x.shape[0], self.num_heads, self.num_kv_heads, self.head_dim
@@ -219,5 +223,6 @@ class SigmoidAttention(Mixer):
                          self.temp_coef, self.temp_every, ctx.positions, ctx.tok_seq, table, hq, hkv, d, gate, write_cache,
                          self.rt.status)
         ops.sigmoid_attention(q, k_pages, v_pages, out, self.head_bias, gate, ctx.q_start, ctx.kv_len, ctx.tok_seq, table,
-                              ctx.num_seqs, ctx.num_decode, ctx.max_q_len, ctx.max_kv_len, self.scale, self.rt.status)
+                              ctx.num_seqs, ctx.num_decode, ctx.max_q_len, ctx.max_kv_len, self.scale, self.rt.status,
+                              partial=self._partial)
         return self.o_proj(out.view(T, hq * d))

@@ -60,7 +60,10 @@ class Replayer:
         return {r: torch.cat(rows) if rows else torch.empty(0) for r, rows in self.rows.items()}
 
 
-def assert_close(got: Dict[Hashable, torch.Tensor], want: Dict[Hashable, torch.Tensor], dtype: str, what: str):
+def assert_close(got: Dict[Hashable, torch.Tensor], want: Dict[Hashable, torch.Tensor], dtype: str, what: str,
+                 tol: float = None):
+    """``tol``: a bound of the caller's own in place of ``TOL[dtype]``."""
+    bound = TOL[dtype] if tol is None else tol
     for req, w in want.items():
         g = got[req]
         assert g.shape == w.shape, f"{what}: request {req}: {tuple(g.shape)} vs {tuple(w.shape)}"
@@ -68,6 +71,6 @@ def assert_close(got: Dict[Hashable, torch.Tensor], want: Dict[Hashable, torch.T
         scale = max(float(w.abs().max()), 1e-6)
         err = (g - w).abs().max(dim=-1).values / scale
         worst = int(err.argmax())
-        assert float(err[worst]) <= TOL[dtype], (
-            f"{what}: request {req}: first position beyond {TOL[dtype]:g} is "
-            f"{int((err > TOL[dtype]).nonzero()[0])}, worst {float(err[worst]):.3g} at position {worst}")
+        assert float(err[worst]) <= bound, (
+            f"{what}: request {req}: first position beyond {bound:g} is "
+            f"{int((err > bound).nonzero()[0])}, worst {float(err[worst]):.3g} at position {worst}")
