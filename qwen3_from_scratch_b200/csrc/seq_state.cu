@@ -58,11 +58,12 @@ __global__ void token_shift_kernel(const float* __restrict__ x, const float* __r
 
 // ---------------------------------------------------------------- short causal convolution per channel
 // grid (tokens, channel chunks).  x: [T, ldx] with the C channels at column x_col; state: [slots, K - 1, C]
-// float32, entry K - 2 the newest.  The state is only read here; conv_state_kernel renews it afterwards.
+// float32, entry K - 2 the newest.  The state of a longer portion is only read here (its first K - 1 tokens read
+// it from several blocks); conv_state_kernel renews it afterwards.
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ in_bias,
                                    const float* __restrict__ w, const float* __restrict__ bias,
-                                   const float* __restrict__ state, const int* __restrict__ q_start,
+                                   float* __restrict__ state, const int* __restrict__ q_start,
                                    const int* __restrict__ tok_seq, const int* __restrict__ slot_ids,
                                    T* __restrict__ out, int C, int K, int act, int num_slots, int* status) {
   pdl_wait();
@@ -78,6 +79,7 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int ldx, const float
     return;
   }
   const int at = t - q_start[b];  // place of the token in its portion
+  const bool single = q_start[b + 1] - q_start[b] == 1;
   const float ib = in_bias ? in_bias[c] : 0.f;
   float acc = bias ? bias[c] : 0.f;
   for (int j = 0; j < K; ++j) {
@@ -88,6 +90,9 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int ldx, const float
     else
       v = state[((size_t)slot * (K - 1) + (K - 1 + at - back)) * C + c];
     acc = fmaf(w[(size_t)c * K + j], v, acc);
+    // a portion of one token: nobody else reads this channel's tail, so it moves up here (what tap j read becomes
+    // entry j - 1) and the renewing kernel leaves the request alone
+    if (single && j > 0) state[((size_t)slot * (K - 1) + j - 1) * C + c] = v;
   }
   out[(size_t)t * C + c] = from_float<T>(activate(acc, act));
 }
@@ -105,6 +110,7 @@ __global__ void conv_state_kernel(const T* __restrict__ x, int ldx, const float*
   const int slot = slot_ids[b];
   if (c >= C || slot < 0 || slot >= num_slots) return;
   const int t0 = q_start[b], n = q_start[b + 1] - t0;
+  if (n == 1) return;  // the convolution kernel has moved a single token's tail itself
   const float ib = in_bias ? in_bias[c] : 0.f;
   float* st = state + (size_t)slot * (K - 1) * C + c;
   for (int i = 0; i < K - 1; ++i) {
@@ -247,6 +253,195 @@ __global__ void selective_scan_kernel(const T* __restrict__ xc, const T* __restr
     if (n < N) st[(size_t)n * I] = S[n];
 }
 
+// ---------------------------------------------------------------- the same recurrences over chunks of a portion
+// A thread per channel walks a whole portion alone, which leaves most of the GPU idle when a long portion of a
+// single request runs: the portion is then cut into chunks of SCAN_CHUNK tokens that run side by side in three
+// launches.  Both recurrences are linear in the state, S_t = a_t S_{t-1} + b_t, so a chunk is summarised by the
+// product P of its a_t and the state V that it reaches from zero; then, chunk after chunk, S_in(j + 1) =
+// P_j S_in(j) + V_j (a loop of portion / SCAN_CHUNK steps), and each chunk is walked again from its S_in.
+// Chunk j of request b is filed at scratch index q_start[b] / SCAN_CHUNK + b + j, which never collides: a
+// request of n tokens has at most n / SCAN_CHUNK + 1 chunks.  The sums differ from the single walk's by float32
+// rounding; the float32 run keeps the single walk, so that its bits do not depend on the cut.
+constexpr int SCAN_CHUNK = 64;
+
+__device__ __forceinline__ void rglru_coeffs(float g_r, float g_i, float rb, float ib, float rate, float u, float& a,
+                                             float& b) {
+  const float r = sigmoid_f(g_r + rb), i = sigmoid_f(g_i + ib);
+  const float log_a = rate * r;
+  a = expf(log_a);
+  b = sqrtf(-expm1f(2.f * log_a)) * i * u;
+}
+
+// PASS 1: the chunk's product and zero-start state into scratch [chunk][2][C].  PASS 3: the walk from the chunk's
+// incoming state (left in scratch [chunk][0][C] by the carry kernel), writing the output.
+template <typename T, int PASS>
+__global__ void rglru_chunk_kernel(const T* __restrict__ proj, int ld_proj, int y_col, const float* __restrict__ y_bias,
+                                   const T* __restrict__ u, const float* __restrict__ gates,
+                                   const float* __restrict__ ra_bias, const float* __restrict__ ri_bias,
+                                   const float* __restrict__ lam, float decay, float* __restrict__ scratch,
+                                   const int* __restrict__ q_start, T* __restrict__ out, int Ttot, int C, int bw) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x, j = blockIdx.y;
+  const int c = blockIdx.z * blockDim.x + threadIdx.x;
+  const int t0 = q_start[b] + j * SCAN_CHUNK, end = q_start[b + 1];
+  if (c >= C || t0 >= end) return;
+  const int t1 = min(end, t0 + SCAN_CHUNK);
+  float* sc = scratch + ((size_t)(q_start[b] / SCAN_CHUNK + b + j) * 2) * C + c;
+  const int blk = c / bw, jj = c - blk * bw;
+  const float rate = -decay * softplus_f(lam[c]);
+  const float rb = ra_bias[c], ib = ri_bias[c], yb = (PASS == 3 && y_bias) ? y_bias[c] : 0.f;
+  float S = PASS == 3 ? sc[0] : 0.f, P = 1.f;
+  const float* g = gates + ((size_t)blk * Ttot + t0) * 2 * bw;
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t, g += 2 * bw) {
+    float a, bb;
+    rglru_coeffs(g[jj], g[bw + jj], rb, ib, rate, to_float(u[(size_t)t * C + c]), a, bb);
+    S = fmaf(a, S, bb);
+    if (PASS == 1) P *= a;
+    if (PASS == 3) {
+      const float y = gelu_tanh_f(to_float(proj[(size_t)t * ld_proj + y_col + c]) + yb);
+      out[(size_t)t * C + c] = from_float<T>(S * y);
+    }
+  }
+  if (PASS == 1) {
+    sc[0] = P;
+    sc[C] = S;
+  }
+}
+
+// grid (requests, channel chunks): scratch [chunk][0] becomes the chunk's incoming state; the request's state slot
+// receives the state after its last chunk.
+__global__ void rglru_carry_kernel(float* __restrict__ scratch, float* __restrict__ state, const int* __restrict__ q_start,
+                                   const int* __restrict__ slot_ids, int C, int num_slots, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int slot = slot_ids[b];
+  const bool live = slot >= 0 && slot < num_slots;
+  if (!live && threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+  const int n = q_start[b + 1] - q_start[b];
+  const int chunks = (n + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  float* sc = scratch + ((size_t)(q_start[b] / SCAN_CHUNK + b) * 2) * C + c;
+  float S = live ? state[(size_t)slot * C + c] : 0.f;
+  for (int j = 0; j < chunks; ++j, sc += 2 * (size_t)C) {
+    const float P = sc[0], V = sc[C];
+    sc[0] = S;
+    S = fmaf(P, S, V);
+  }
+  if (live) state[(size_t)slot * C + c] = S;
+}
+
+// Selective scan by chunks.  scratch [chunk][N + 1][I]: PASS 1 leaves the zero-start state per n and, at n = N, the
+// chunk's sum of step sizes (the chunk's product of exp(step A[c, n]) is exp(A[c, n] * that sum)); the carry kernel
+// turns the N entries into the incoming state; PASS 3 walks the chunk from it and writes the output.
+template <typename T, int NMAX, int PASS>
+__global__ void selective_chunk_kernel(const T* __restrict__ xc, const T* __restrict__ proj, int ld_proj, int z_col,
+                                       const float* __restrict__ bc, const float* __restrict__ dt,
+                                       const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                       const float* __restrict__ Dp, float* __restrict__ scratch,
+                                       const int* __restrict__ q_start, T* __restrict__ out, int I, int N) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x, j = blockIdx.y;
+  const int c = blockIdx.z * blockDim.x + threadIdx.x;
+  const int t0 = q_start[b] + j * SCAN_CHUNK, end = q_start[b + 1];
+  if (c >= I || t0 >= end) return;
+  const int t1 = min(end, t0 + SCAN_CHUNK);
+  float* sc = scratch + ((size_t)(q_start[b] / SCAN_CHUNK + b + j) * (N + 1)) * I + c;
+  float A[NMAX], S[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) {
+    A[n] = n < N ? -expf(A_log[(size_t)c * N + n]) : 0.f;
+    S[n] = (PASS == 3 && n < N) ? sc[(size_t)n * I] : 0.f;
+  }
+  const float db = dt_bias[c], dskip = PASS == 3 ? Dp[c] : 0.f;
+  float sum_step = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const float step = softplus_f(dt[(size_t)t * I + c] + db);
+    const float x = to_float(xc[(size_t)t * I + c]);
+    const float sx = step * x;
+    const float* Bt = bc + (size_t)t * 2 * N;
+    const float* Ct = Bt + N;
+    float y = 0.f;
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      if (n < N) {
+        S[n] = fmaf(expf(step * A[n]), S[n], sx * Bt[n]);
+        if (PASS == 3) y = fmaf(S[n], Ct[n], y);
+      }
+    }
+    if (PASS == 1) sum_step += step;
+    if (PASS == 3) {
+      y = fmaf(dskip, x, y);
+      const float z = to_float(proj[(size_t)t * ld_proj + z_col + c]);
+      out[(size_t)t * I + c] = from_float<T>(y * silu_f(z));
+    }
+  }
+  if (PASS == 1) {
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n)
+      if (n < N) sc[(size_t)n * I] = S[n];
+    sc[(size_t)N * I] = sum_step;
+  }
+}
+
+// grid (requests, channel chunks, N): one thread per (channel, n).
+__global__ void selective_carry_kernel(float* __restrict__ scratch, const float* __restrict__ A_log,
+                                       float* __restrict__ state, const int* __restrict__ q_start,
+                                       const int* __restrict__ slot_ids, int I, int N, int num_slots, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x, n = blockIdx.z;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= I) return;
+  const int slot = slot_ids[b];
+  const bool live = slot >= 0 && slot < num_slots;
+  if (!live && threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+  const int len = q_start[b + 1] - q_start[b];
+  const int chunks = (len + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  const float A = -expf(A_log[(size_t)c * N + n]);
+  float* sc = scratch + ((size_t)(q_start[b] / SCAN_CHUNK + b) * (N + 1)) * I + c;
+  float* st = state + ((size_t)slot * N + n) * I + c;
+  float S = live ? *st : 0.f;
+  for (int j = 0; j < chunks; ++j, sc += (size_t)(N + 1) * I) {
+    const float V = sc[(size_t)n * I], P = expf(A * sc[(size_t)N * I]);
+    sc[(size_t)n * I] = S;
+    S = fmaf(P, S, V);
+  }
+  if (live) *st = S;
+}
+
+template <typename T>
+static int selective_chunked_launch(const void* xc, const void* proj, int ld_proj, int z_col, const float* bc,
+                                    const float* dt, const float* dt_bias, const float* A_log, const float* Dp,
+                                    float* state, float* scratch, const int* q_start, const int* slot_ids, void* out,
+                                    int B, int max_q_len, int I, int N, int num_slots, int* status, cudaStream_t stream) {
+  const int threads = 64;
+  const int chunks = (max_q_len + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  dim3 grid(B, chunks, (I + threads - 1) / threads), cgrid(B, (I + threads - 1) / threads, N);
+  if (chunks > 65535 || grid.z > 65535 || N > 65535) return Q3_ERR_SIZE;
+#define Q3_SC(NM)                                                                                                    \
+  do {                                                                                                               \
+    q3::launch(selective_chunk_kernel<T, NM, 1>, grid, dim3(threads), 0, stream, (const T*)xc, (const T*)proj, ld_proj, \
+               z_col, bc, dt, dt_bias, A_log, Dp, scratch, q_start, (T*)out, I, N);                                  \
+    q3::launch(selective_carry_kernel, cgrid, dim3(threads), 0, stream, scratch, A_log, state, q_start, slot_ids, I, N, \
+               num_slots, status);                                                                                   \
+    q3::launch(selective_chunk_kernel<T, NM, 3>, grid, dim3(threads), 0, stream, (const T*)xc, (const T*)proj, ld_proj, \
+               z_col, bc, dt, dt_bias, A_log, Dp, scratch, q_start, (T*)out, I, N);                                  \
+  } while (0)
+  if (N <= 8) Q3_SC(8);
+  else if (N <= 16) Q3_SC(16);
+  else if (N <= 32) Q3_SC(32);
+  else if (N <= 64) Q3_SC(64);
+  else if (N <= 128) Q3_SC(128);
+  else return Q3_ERR_SIZE;
+#undef Q3_SC
+  return launch_status();
+}
+
 template <typename T>
 static int selective_scan_launch(const void* xc, const void* proj, int ld_proj, int z_col, const float* bc, const float* dt,
                                  const float* dt_bias, const float* A_log, const float* Dp, float* state,
@@ -286,7 +481,7 @@ extern "C" int q3_token_shift(const float* x, const float* mu, float* state, con
   return q3::launch_status();
 }
 
-// The convolution of a step's tokens, then the state's renewal (two launches).  x: [T, ldx] in `dtype`, the
+// The convolution of a step's tokens, then the state's renewal (a second launch unless every portion is one token).  x: [T, ldx] in `dtype`, the
 // channels at x (the caller offsets the pointer); w: float32 [C, K]; state: float32 [num_slots, K - 1, C].
 extern "C" int q3_causal_conv(const void* x, int ldx, const float* in_bias, const float* w, const float* bias, float* state,
                               const int* q_start, const int* tok_seq, const int* slot_ids, void* out, int dtype, int T,
@@ -297,9 +492,9 @@ extern "C" int q3_causal_conv(const void* x, int ldx, const float* in_bias, cons
   dim3 grid(T, (C + threads - 1) / threads), sgrid(B, (C + threads - 1) / threads);
   if (grid.y > 65535) return Q3_ERR_SIZE;
   Q3_BY_DTYPE(dtype, {
-    q3::launch(q3::causal_conv_kernel<E>, grid, dim3(threads), 0, stream, (const E*)x, ldx, in_bias, w, bias,
-               (const float*)state, q_start, tok_seq, slot_ids, (E*)out, C, K, act, num_slots, status);
-    if (K > 1)
+    q3::launch(q3::causal_conv_kernel<E>, grid, dim3(threads), 0, stream, (const E*)x, ldx, in_bias, w, bias, state,
+               q_start, tok_seq, slot_ids, (E*)out, C, K, act, num_slots, status);
+    if (K > 1 && T > B)  // T == B: every portion is a single token
       q3::launch(q3::conv_state_kernel<E>, sgrid, dim3(threads), 0, stream, (const E*)x, ldx, in_bias, state, q_start,
                  slot_ids, C, K, num_slots);
   })
@@ -342,4 +537,43 @@ extern "C" int q3_selective_scan(const void* xc, const void* proj, int ld_proj, 
   if (N <= 0) return Q3_ERR_SIZE;
   Q3_BY_DTYPE(dtype, return q3::selective_scan_launch<E>(xc, proj, ld_proj, z_col, bc, dt, dt_bias, A_log, Dp, state, q_start,
                                                          slot_ids, out, B, I, N, num_slots, status, stream))
+}
+
+// Tokens per chunk of the chunked scans; their scratch holds (tokens / chunk + requests + 1) chunk records.
+extern "C" int q3_scan_chunk() { return q3::SCAN_CHUNK; }
+
+// rglru_scan over chunks of the portions (three launches).  scratch: float32, 2 * C per chunk record.
+extern "C" int q3_rglru_scan_chunked(const void* proj, int ld_proj, int y_col, const float* y_bias, const void* u,
+                                     const float* gates, const float* ra_bias, const float* ri_bias, const float* lam,
+                                     float decay, float* state, float* scratch, const int* q_start, const int* slot_ids,
+                                     void* out, int dtype, int T, int B, int max_q_len, int C, int bw, int num_slots,
+                                     int* status, cudaStream_t stream) {
+  if (T <= 0 || B <= 0 || C <= 0 || max_q_len <= 0) return 0;
+  if (bw <= 0 || C % bw) return Q3_ERR_SIZE;
+  const int threads = 64;
+  const int chunks = (max_q_len + q3::SCAN_CHUNK - 1) / q3::SCAN_CHUNK;
+  dim3 grid(B, chunks, (C + threads - 1) / threads), cgrid(B, (C + threads - 1) / threads);
+  if (chunks > 65535 || grid.z > 65535) return Q3_ERR_SIZE;
+  Q3_BY_DTYPE(dtype, {
+    q3::launch(q3::rglru_chunk_kernel<E, 1>, grid, dim3(threads), 0, stream, (const E*)proj, ld_proj, y_col, y_bias,
+               (const E*)u, gates, ra_bias, ri_bias, lam, decay, scratch, q_start, (E*)out, T, C, bw);
+    q3::launch(q3::rglru_carry_kernel, cgrid, dim3(threads), 0, stream, scratch, state, q_start, slot_ids, C, num_slots,
+               status);
+    q3::launch(q3::rglru_chunk_kernel<E, 3>, grid, dim3(threads), 0, stream, (const E*)proj, ld_proj, y_col, y_bias,
+               (const E*)u, gates, ra_bias, ri_bias, lam, decay, scratch, q_start, (E*)out, T, C, bw);
+  })
+  return q3::launch_status();
+}
+
+// selective_scan over chunks of the portions (three launches).  scratch: float32, (N + 1) * I per chunk record.
+extern "C" int q3_selective_scan_chunked(const void* xc, const void* proj, int ld_proj, int z_col, const float* bc,
+                                         const float* dt, const float* dt_bias, const float* A_log, const float* Dp,
+                                         float* state, float* scratch, const int* q_start, const int* slot_ids, void* out,
+                                         int dtype, int T, int B, int max_q_len, int I, int N, int num_slots, int* status,
+                                         cudaStream_t stream) {
+  if (T <= 0 || B <= 0 || I <= 0 || max_q_len <= 0) return 0;
+  if (N <= 0) return Q3_ERR_SIZE;
+  Q3_BY_DTYPE(dtype, return q3::selective_chunked_launch<E>(xc, proj, ld_proj, z_col, bc, dt, dt_bias, A_log, Dp, state,
+                                                            scratch, q_start, slot_ids, out, B, max_q_len, I, N, num_slots,
+                                                            status, stream))
 }

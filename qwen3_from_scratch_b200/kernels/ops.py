@@ -93,6 +93,12 @@ _SIGNATURES = {
     "q3_rglru_scan": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                       _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                       _c_int, _c_void_p, _c_void_p],
+    "q3_rglru_scan_chunked": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                              _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                              _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "q3_selective_scan_chunked": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                  _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                                  _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "q3_selective_scan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_void_p, _c_void_p],
@@ -134,6 +140,8 @@ def library() -> ctypes.CDLL:
                 lib.q3_sm_count.restype = _c_int
                 lib.q3_attn_decode_blocks_per_sm.argtypes = [_c_int]
                 lib.q3_attn_decode_blocks_per_sm.restype = _c_int
+                lib.q3_scan_chunk.argtypes = []
+                lib.q3_scan_chunk.restype = _c_int
                 lib.q3_sample_scratch_bytes.argtypes = [_c_int]
                 lib.q3_sample_scratch_bytes.restype = _c_ll
                 _lib, _lib_path = _Counting(lib), path
@@ -979,14 +987,34 @@ def block_diag(u: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None
     _done("block_diag", code, f"blocks {nb} of {bw}")
 
 
+def scan_chunk() -> int:
+    """Tokens per chunk of the chunked scans."""
+    if "scan chunk" not in _DEVICE_FACTS:
+        _DEVICE_FACTS["scan chunk"] = int(library()._lib.q3_scan_chunk())
+    return _DEVICE_FACTS["scan chunk"]
+
+
+def scan_chunk_records(num_tokens: int, num_seqs: int) -> int:
+    """Chunk records that the chunked scans' scratch must hold for a step of so many tokens and requests."""
+    return num_tokens // scan_chunk() + num_seqs + 1
+
+
+def scan_chunked_pays(dtype: torch.dtype, max_q_len: int) -> bool:
+    """Whether a step's recurrences run over chunks of their portions: bfloat16 runs with a portion of at least
+    four chunks.  A thread per channel that walks a whole portion keeps few SMs busy; the float32 run keeps that
+    walk all the same, so that its bits do not depend on how a prompt was cut."""
+    return dtype == torch.bfloat16 and max_q_len >= 4 * scan_chunk()
+
+
 def rglru_scan(proj: torch.Tensor, y_column: int, y_bias: Optional[torch.Tensor], u: torch.Tensor, gates: torch.Tensor,
                ra_bias: torch.Tensor, ri_bias: torch.Tensor, lam: torch.Tensor, decay: float, state: torch.Tensor,
                q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor,
-               status: torch.Tensor) -> None:
+               status: torch.Tensor, max_q_len: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
     """The gated linear recurrence S = a S + sqrt(1 - a^2) (i * u) with a = exp(-decay * softplus(lam) * r),
     r and i the sigmoids of ``gates`` (float32 [blocks, T, 2 bw]: per block the recurrence gate's rows, then the
     input gate's) plus their biases; out = S * gelu_tanh(proj[:, y_column : y_column + C] + y_bias).  ``state``:
-    float32 [slots, C]."""
+    float32 [slots, C].  With ``scratch`` (float32, ``scan_chunk_records(T, num_seqs) * 2 * C``) and a longest
+    portion ``max_q_len`` of ``scan_chunked_pays`` the portions are cut into chunks that run side by side."""
     _check("rglru_scan.proj", proj)
     _check("rglru_scan.u", u, proj.dtype)
     _check("rglru_scan.out", out, proj.dtype)
@@ -1002,6 +1030,17 @@ def rglru_scan(proj: torch.Tensor, y_column: int, y_bias: Optional[torch.Tensor]
             or y_column + C > proj.shape[1] or state.dim() != 2 or state.shape[1] != C):
         raise KernelError(f"rglru_scan: proj {tuple(proj.shape)}, u {tuple(u.shape)}, gates {tuple(gates.shape)}, "
                           f"state {tuple(state.shape)}")
+    if scratch is not None and scan_chunked_pays(proj.dtype, max_q_len):
+        _check("rglru_scan.scratch", scratch, torch.float32)
+        if scratch.numel() < scan_chunk_records(T, num_seqs) * 2 * C:
+            raise KernelError(f"rglru_scan: scratch of {scratch.numel()} floats for {T} tokens of {num_seqs} requests")
+        code = library().q3_rglru_scan_chunked(
+            proj.data_ptr(), proj.shape[1], int(y_column), _ptr(y_bias), u.data_ptr(), gates.data_ptr(),
+            ra_bias.data_ptr(), ri_bias.data_ptr(), lam.data_ptr(), float(decay), state.data_ptr(), scratch.data_ptr(),
+            q_start.data_ptr(), slot_ids.data_ptr(), out.data_ptr(), dtype_tag(proj.dtype), T, int(num_seqs),
+            int(max_q_len), C, two_bw // 2, state.shape[0], status.data_ptr(), _stream())
+        _done("rglru_scan (chunked)", code, f"channels {C}")
+        return
     code = library().q3_rglru_scan(proj.data_ptr(), proj.shape[1], int(y_column), _ptr(y_bias), u.data_ptr(),
                                    gates.data_ptr(), ra_bias.data_ptr(), ri_bias.data_ptr(), lam.data_ptr(), float(decay),
                                    state.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(), out.data_ptr(),
@@ -1013,10 +1052,11 @@ def rglru_scan(proj: torch.Tensor, y_column: int, y_bias: Optional[torch.Tensor]
 def selective_scan(xc: torch.Tensor, proj: torch.Tensor, z_column: int, bc: torch.Tensor, dt: torch.Tensor,
                    dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor,
                    q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor,
-                   status: torch.Tensor) -> None:
+                   status: torch.Tensor, max_q_len: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
     """The selective scan: per channel c and state n, S = exp(step A[c, n]) S + step x B[n], y = sum_n S C[n] +
     D x, out = y * silu(z); step = softplus(dt + dt_bias), A = -exp(a_log), z = proj[:, z_column : z_column + I];
-    bc: float32 [T, 2 N] (B then C); dt: float32 [T, I]; state: float32 [slots, N, I]."""
+    bc: float32 [T, 2 N] (B then C); dt: float32 [T, I]; state: float32 [slots, N, I].  ``scratch`` (float32,
+    ``scan_chunk_records(T, num_seqs) * (N + 1) * I``) and ``max_q_len``: as in ``rglru_scan``."""
     _check("selective_scan.xc", xc)
     _check("selective_scan.proj", proj, xc.dtype)
     _check("selective_scan.out", out, xc.dtype)
@@ -1029,6 +1069,17 @@ def selective_scan(xc: torch.Tensor, proj: torch.Tensor, z_column: int, bc: torc
             or z_column + I > proj.shape[1] or state.dim() != 3 or tuple(state.shape[1:]) != (N, I)):
         raise KernelError(f"selective_scan: x {tuple(xc.shape)}, proj {tuple(proj.shape)}, bc {tuple(bc.shape)}, dt "
                           f"{tuple(dt.shape)}, A {tuple(a_log.shape)}, state {tuple(state.shape)}")
+    if scratch is not None and scan_chunked_pays(xc.dtype, max_q_len):
+        _check("selective_scan.scratch", scratch, torch.float32)
+        if scratch.numel() < scan_chunk_records(T, num_seqs) * (N + 1) * I:
+            raise KernelError(f"selective_scan: scratch of {scratch.numel()} floats for {T} tokens of {num_seqs} requests")
+        code = library().q3_selective_scan_chunked(
+            xc.data_ptr(), proj.data_ptr(), proj.shape[1], int(z_column), bc.data_ptr(), dt.data_ptr(), dt_bias.data_ptr(),
+            a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), scratch.data_ptr(), q_start.data_ptr(),
+            slot_ids.data_ptr(), out.data_ptr(), dtype_tag(xc.dtype), T, int(num_seqs), int(max_q_len), I, N,
+            state.shape[0], status.data_ptr(), _stream())
+        _done("selective_scan (chunked)", code, f"channels {I}, state {N}")
+        return
     code = library().q3_selective_scan(xc.data_ptr(), proj.data_ptr(), proj.shape[1], int(z_column), bc.data_ptr(),
                                        dt.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(),
                                        state.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(), out.data_ptr(),

@@ -87,6 +87,10 @@ class RGLRU(Mixer, _NamedTensors):
         self._u = rt.shared("rglru.u", rt.max_tokens, c)
         self._gates = rt.shared("rglru.gates", rt.max_tokens * 2 * c, dtype=torch.float32)
         self._gated = rt.shared("rglru.gated", rt.max_tokens, c)
+        self._chunks = None
+        if rt.dtype == torch.bfloat16:
+            self._chunks = rt.shared("rglru.chunks", ops.scan_chunk_records(rt.max_tokens, rt.max_seqs) * 2 * c,
+                                     dtype=torch.float32)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         T, c, bw = x.shape[0], self.width, self.block_width
@@ -99,7 +103,8 @@ class RGLRU(Mixer, _NamedTensors):
         ops.block_diag(u, self.gate_weight, gates)
         gated = self._gated[:T]
         ops.rglru_scan(proj, 0, self.y_bias, u, gates, self.gate_a_bias, self.gate_i_bias, self.lam, self.decay,
-                       ctx.state(cache_id, "state"), ctx.q_start, ctx.slot_ids, ctx.num_seqs, gated, status)
+                       ctx.state(cache_id, "state"), ctx.q_start, ctx.slot_ids, ctx.num_seqs, gated, status,
+                       max_q_len=ctx.max_q_len, scratch=self._chunks)
         return self.out_proj(gated)
 
 
@@ -147,6 +152,10 @@ class SelectiveScan(Mixer, _NamedTensors):
         self.out_proj = Linear(weights.pop(t["out"]), rt, tag="scan.out")
         self._xc = rt.shared("scan.xc", rt.max_tokens, i)
         self._y = rt.shared("scan.y", rt.max_tokens, i)
+        self._chunks = None
+        if rt.dtype == torch.bfloat16:
+            self._chunks = rt.shared("scan.chunks", ops.scan_chunk_records(rt.max_tokens, rt.max_seqs) * (n + 1) * i,
+                                     dtype=torch.float32)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         T, i = x.shape[0], self.inner
@@ -159,5 +168,6 @@ class SelectiveScan(Mixer, _NamedTensors):
         dt = self.dt_proj(self.dt_low(xc))
         y = self._y[:T]
         ops.selective_scan(xc, proj, i, bc, dt, self.dt_bias, self.a_log, self.d_skip, ctx.state(cache_id, "state"),
-                           ctx.q_start, ctx.slot_ids, ctx.num_seqs, y, status)
+                           ctx.q_start, ctx.slot_ids, ctx.num_seqs, y, status, max_q_len=ctx.max_q_len,
+                           scratch=self._chunks)
         return self.out_proj(y)
