@@ -765,6 +765,10 @@ def main() -> int:
     p.add_argument("--only-rows", type=int, default=None, help="with --profile products: one number of rows")
     p.add_argument("--leave-out", action="store_true",
                    help="with --profile: time the step as a CUDA graph, whole and with each kind of kernel left out")
+    p.add_argument("--arch", choices=["binupel"], default=None,
+                   help="instead of the default workload: that design beside Qwen3 at equal layer sizes (a prompt step "
+                        "and two decode batches, every kernel of a step timed on its own); see bench_arch.py")
+    p.add_argument("--arch-size", default="2k", choices=["2k", "4k"], help="with --arch: the layer sizes")
     p.add_argument("--profile", choices=["decode", "prefill", "products"], default=None,
                    help="short run for a profiler instead of the benchmark (see profile())")
     args = p.parse_args()
@@ -773,6 +777,15 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.arch:
+        import bench_arch
+
+        def sample_clocks():
+            sampler = ClockSampler()
+            sampler.start()
+            return sampler
+
+        return bench_arch.compare(args, load_peaks(), sample_clocks)
     if args.profile == "products":
         return profile_products(args)
     if args.profile:

@@ -1,0 +1,262 @@
+"""``bench.py --arch binupel``: the Binupel design beside Qwen3 at equal layer sizes (random weights drawn on
+the device): a prompt step of 2,048 tokens and decode steps at two batch sizes, each replayed on the device
+between CUDA events, and every kernel of one eagerly launched step timed by events of its own, with the bytes
+or flops it must move and the fraction of the measured copy bandwidth or bf16 throughput that this makes.
+
+A Binupel model of ``layers`` entries repeats the pattern selective scan, RG-LRU, attention; the Qwen3 model
+has as many layers of the same width, heads, head size and feed-forward width.
+"""
+
+from __future__ import annotations
+
+import json
+import statistics
+import sys
+import tempfile
+import time
+
+SIZES = {
+    # width, feed-forward, heads, kv heads, head size, vocabulary, layers
+    "2k": dict(width=2048, ff=6144, heads=16, kv_heads=8, dim=128, vocab=32000, layers=12),
+    "4k": dict(width=4096, ff=12288, heads=32, kv_heads=8, dim=128, vocab=32000, layers=6),
+}
+PAGE = 16
+
+
+def binupel_config(s):
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"],
+                                          "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+                                          "q_temp": {"coef": 0.5, "every": 128}},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    rec = {"type": "rglru", "mixer": {"width": s["width"], "blocks": s["width"] // 256, "conv": 4},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    scan = {"type": "mamba1", "mixer": {"inner": 2 * s["width"], "state": 16, "dt_rank": s["width"] // 16, "conv": 4},
+            "mlp": {"kind": "dense", "ff": s["ff"]}}
+    pattern = [scan, rec, att]
+    return {"architecture": "Binupel", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "postln_alpha": 2.0, "layers": [pattern[i % 3] for i in range(s["layers"])]}
+
+
+def qwen3_config(s):
+    return dict(architectures=["Qwen3ForCausalLM"], vocab_size=s["vocab"], hidden_size=s["width"], hidden_act="silu",
+                num_hidden_layers=s["layers"], max_position_embeddings=40960, num_key_value_heads=s["kv_heads"],
+                num_attention_heads=s["heads"], head_dim=s["dim"], intermediate_size=s["ff"], rms_norm_eps=1e-6,
+                rope_theta=1000000.0, tie_word_embeddings=False)
+
+
+def make_session(config, max_seqs, pool_tokens, step_tokens):
+    from qwen3_from_scratch_b200.engine.session import Session
+    from qwen3_from_scratch_b200.registry import config_from_dict
+    with tempfile.TemporaryDirectory(prefix="q3b200-arch-") as tmp:
+        config_from_dict(config).save(tmp)
+        return Session(tmp, dtype="bfloat16", page_size=PAGE, num_pages=pool_tokens // PAGE + max_seqs, max_seqs=max_seqs,
+                       max_step_tokens=step_tokens, random_weights=0)
+
+
+def time_replays(session, steps, warmup):
+    """Median milliseconds of one replay of the session's last step (a CUDA graph once its shape has come
+    twice), every replay between events of its own; a buffer larger than L2 is written between replays."""
+    import torch
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        session.rerun_last()
+    out = []
+    for _ in range(steps):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        session.rerun_last()
+        end.record()
+        torch.cuda.synchronize()
+        out.append(start.elapsed_time(end))
+    return statistics.median(out)
+
+
+class KernelClock:
+    """Wraps the launchers of ``kernels.ops`` (and the projections' library products) with CUDA events and the
+    work each call must do, for one eagerly launched step."""
+
+    def __init__(self, scenario):
+        self.scenario = scenario
+        self.rows = {}
+        self.pending = []
+        self.saved = []
+
+    # what a call must move: ("bytes", n) against the copy bandwidth or ("flops", n) against the bf16 peak
+    def work(self, name, a, k):
+        sc = self.scenario
+        size = lambda t: t.numel() * t.element_size()  # noqa: E731
+        if name in ("add_rmsnorm", "scale_add_rmsnorm"):
+            resid, delta, out = a[0], a[1], a[3]
+            n = size(resid) * (2 if (delta is not None or name == "scale_add_rmsnorm") else 1)
+            return "bytes", n + (size(delta) if delta is not None else 0) + (size(out) if out is not None else 0)
+        if name == "add_rmsnorm_rows":
+            return "bytes", size(a[4]) * 3
+        if name == "token_shift":
+            return "bytes", size(a[0]) + size(a[6])
+        if name == "causal_conv":
+            return "bytes", 2 * size(a[10])
+        if name in ("gated_act", "swiglu"):
+            return "bytes", size(a[0]) + size(a[1])
+        if name == "qk_gate_post":
+            proj, q_out, pages = a[0], a[1], a[2]
+            return "bytes", size(proj) + size(q_out) + 2 * proj.shape[0] * pages.shape[1] * pages.shape[3] * proj.element_size()
+        if name == "qkv_post":
+            qkv, q_out, pages = a[0], a[1], a[2]
+            return "bytes", size(qkv) + size(q_out) + 2 * qkv.shape[0] * pages.shape[1] * pages.shape[3] * qkv.element_size()
+        if name == "gemm_tc_qkv":
+            x, w = a[0], a[1]
+            return "flops", 2 * x.shape[0] * w.shape[0] * w.shape[1]
+        if name == "rglru_scan":
+            u, gates, out = a[3], a[4], a[13]
+            twice = 2 if k.get("scratch") is not None and sc["kind"] == "prefill" else 1
+            return "bytes", twice * (size(gates) + size(u)) + size(u) + size(out)
+        if name == "selective_scan":
+            xc, bc, dt, out = a[0], a[3], a[4], a[12]
+            twice = 2 if k.get("scratch") is not None and sc["kind"] == "prefill" else 1
+            return "bytes", twice * (size(xc) + size(bc) + size(dt)) + size(xc) + size(out)
+        if name in ("sigmoid_attention", "paged_attention"):
+            q, pages = a[0], a[1]
+            hq, d, hkv = q.shape[1], q.shape[2], pages.shape[1]
+            if sc["kind"] == "prefill":
+                return "flops", 4 * hq * d * sc["tokens"] * (sc["tokens"] + 1) // 2
+            return "bytes", sc["batch"] * sc["context"] * hkv * d * 2 * pages.element_size() + 2 * size(q)
+        if name == "block_diag":
+            u, w = a[0], a[1]
+            if u.shape[0] <= 16:
+                return "bytes", size(w)
+            return "flops", 2 * u.shape[0] * w.shape[0] * w.shape[1] * w.shape[2]
+        if name in ("gemm_skinny", "gemm_skinny_normed", "gemm_skinny_into_stream"):
+            w = a[1] if name != "gemm_skinny_normed" else a[4]
+            return "bytes", size(w)
+        if name == "gemm_tc":
+            return "flops", 2 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
+        if name == "library product":
+            x, w = a
+            if x.shape[0] <= 64:
+                return "bytes", size(w)
+            return "flops", 2 * x.shape[0] * w.shape[0] * w.shape[1]
+        if name == "embed":
+            return "bytes", size(a[2]) * 1.5
+        return "bytes", 0
+
+    def wrap(self, owner, attr, name):
+        import torch
+        real = getattr(owner, attr)
+
+        def timed(*a, **k):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = real(*a, **k)
+            end.record()
+            self.pending.append((name, start, end, self.work(name, a, k)))
+            return out
+
+        self.saved.append((owner, attr, real))
+        setattr(owner, attr, timed)
+
+    def __enter__(self):
+        import torch
+        from qwen3_from_scratch_b200.kernels import ops
+        for name in ("embed", "add_rmsnorm", "add_rmsnorm_rows", "scale_add_rmsnorm", "token_shift", "causal_conv",
+                     "gated_act", "swiglu", "qk_gate_post", "qkv_post", "gemm_tc_qkv", "rglru_scan", "selective_scan",
+                     "sigmoid_attention", "paged_attention", "block_diag", "gemm_skinny", "gemm_skinny_normed",
+                     "gemm_skinny_into_stream", "gemm_tc"):
+            self.wrap(ops, name, name)
+        real_mm = torch.mm
+        clock = self
+
+        def mm(x, wt, **k):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = real_mm(x, wt, **k)
+            end.record()
+            clock.pending.append(("library product", start, end, clock.work("library product", (x, wt.t()), {})))
+            return out
+
+        self.saved.append((torch, "mm", real_mm))
+        torch.mm = mm
+        return self
+
+    def __exit__(self, *exc):
+        import torch
+        for owner, attr, real in self.saved:
+            setattr(owner, attr, real)
+        torch.cuda.synchronize()
+        for name, start, end, (kind, amount) in self.pending:
+            row = self.rows.setdefault((name, kind), {"calls": 0, "us": 0.0, "work": 0.0})
+            row["calls"] += 1
+            row["us"] += start.elapsed_time(end) * 1e3
+            row["work"] += amount
+
+    def table(self, peaks):
+        out = {}
+        for (name, kind), row in sorted(self.rows.items(), key=lambda kv: -kv[1]["us"]):
+            rate = row["work"] / (row["us"] * 1e-6) if row["us"] > 0 else 0.0
+            peak = peaks["hbm_gbs"] * 1e9 if kind == "bytes" else peaks["bf16_tflops"] * 1e12
+            out[f"{name} ({'HBM' if kind == 'bytes' else 'bf16'})"] = {
+                "calls": row["calls"], "us": round(row["us"], 1), "fraction_of_measured_peak": round(rate / peak, 3)}
+        return out
+
+
+def run_scenario(config, scenario, steps, warmup, peaks):
+    """One model in one scenario: the step's time replayed, and its kernels' times in an eager launch."""
+    import torch
+    from qwen3_from_scratch_b200.engine.batch import BatchContext, Entry
+    vocab = config.get("vocab", config.get("vocab_size"))
+    g = torch.Generator().manual_seed(5)
+    ids = lambda n: torch.randint(0, vocab, (n,), generator=g).tolist()  # noqa: E731
+    if scenario["kind"] == "prefill":
+        T = scenario["tokens"]
+        session = make_session(config, 2, T + 64, T)
+        entries = [Entry("p", ids(T), [T - 1])]
+        session.prepare(entries)
+        for _ in range(3):  # the shape's second appearance records its graph
+            session._run(entries)
+        tokens = T
+    else:
+        B, C = scenario["batch"], scenario["context"]
+        session = make_session(config, B, B * (C + PAGE), 2048)
+        for b in range(B):
+            left = C - 1
+            while left > 0:
+                n = min(left, 2048)
+                session.step([Entry(b, ids(n), [])])
+                left -= n
+        entries = [Entry(b, ids(1), [0]) for b in range(B)]
+        session.prepare(entries)
+        for _ in range(3):
+            session._run(entries)
+        tokens = B
+    torch.cuda.synchronize()
+    ms = time_replays(session, steps, warmup)
+    with KernelClock(scenario) as clock:
+        ctx = BatchContext(session.manager, session.storage, session.rt).build(entries, session.vocab_size)
+        session.model.step(ctx)
+    session.check_status()
+    result = {"ms_per_step": round(ms, 4), "tokens_per_s": round(tokens / (ms * 1e-3), 1),
+              "graph": session.last_graph is not None, "kernels": clock.table(peaks)}
+    del session
+    torch.cuda.empty_cache()
+    return result
+
+
+def compare(args, peaks, sample_clocks):
+    size = SIZES[args.arch_size]
+    scenarios = {"prefill_2048": {"kind": "prefill", "tokens": 2048},
+                 "decode_b8_ctx2048": {"kind": "decode", "batch": 8, "context": 2048},
+                 "decode_b64_ctx2048": {"kind": "decode", "batch": 64, "context": 2048}}
+    sampler = sample_clocks()
+    t0 = time.time()
+    out = {"arch": "binupel", "beside": "qwen3", "sizes": dict(size, name=args.arch_size), "dtype": "bf16",
+           "data": "synthetic tokens, random weights drawn on the device", "steps": args.steps, "warmup": args.warmup,
+           "peaks": peaks, "timing": "CUDA events around each replay of the step; 256 MB written between replays",
+           "binupel": {}, "qwen3": {}}
+    for name, scenario in scenarios.items():
+        for model, config in (("binupel", binupel_config(size)), ("qwen3", qwen3_config(size))):
+            out[model][name] = run_scenario(config, scenario, args.steps, args.warmup, peaks)
+            print(f"[bench] {model} {name}: {out[model][name]['ms_per_step']} ms", file=sys.stderr, flush=True)
+    out["clocks"] = sampler.stop()
+    out["seconds"] = round(time.time() - t0, 1)
+    print(json.dumps(out))
+    return 0

@@ -56,13 +56,17 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
   return (uint32_t)row * 128u + ((((uint32_t)col >> 3) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)col & 7u) << 1);
 }
 
-template <int D>
+// SIGMOID: the weights are not normalised over the keys (attn_sigmoid.cu): a visible key gets
+// sigmoid(s * scale + head_bias[h]), there is no maximum, no denominator and nothing to rescale, and the finished
+// row is multiplied by gate[t, h].  The "softmax" threads then only turn scores into weights.
+template <int D, bool SIGMOID = false>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                const int* __restrict__ q_start, const int* __restrict__ kv_len,
                const int* __restrict__ block_table, int table_stride, int page_size, int num_pages, int Hq,
-               int Hkv, float scale_log2, int* status) {
+               int Hkv, float scale_log2, int* status, const float* __restrict__ head_bias = nullptr,
+               const float* __restrict__ gate = nullptr) {
   using S = AttnTcShape<D>;
   constexpr int ATOMS = S::ATOMS;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -275,6 +279,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int soft_tid = threadIdx.x;  // 0 .. 511
     float m_ref = -INFINITY, l = 0.f;
+    // SIGMOID: the head's bias in the units of the base-2 exponential
+    const float bias_log2 = (SIGMOID && head_bias && valid_row) ? head_bias[hk * g + R % g] * 1.4426950408889634f : 0.f;
     bool ok = true;
     // Every softmax thread runs every iteration and meets the others at the named barrier even
     // after a wait has run out (the barrier itself cannot time out); `ok` only switches the work off.
@@ -287,6 +293,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       tmem_ld_32(tmem_s + st * AT_BN + part * AT_PART + lane_base, sv);
       tmem_wait_ld();
       const int base_n = j * AT_BN + part * AT_PART;
+      if constexpr (SIGMOID) {
+        // a thread's packed weights go where another thread's scores were: all scores are in registers first
+        asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX) : "memory");
+        const bool diagonal = j * AT_BN + AT_BN - 1 > pos_first;
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float x0 = fmaf(__uint_as_float(sv[2 * e]), scale_log2, bias_log2);
+          const float x1 = fmaf(__uint_as_float(sv[2 * e + 1]), scale_log2, bias_log2);
+          float p0 = __fdividef(1.0f, 1.0f + ex2_approx(-x0)), p1 = __fdividef(1.0f, 1.0f + ex2_approx(-x1));
+          if (diagonal) {  // keys beyond this row's position (and beyond the sequence) weigh exactly nothing
+            if (base_n + 2 * e > my_pos) p0 = 0.f;
+            if (base_n + 2 * e + 1 > my_pos) p1 = 0.f;
+          }
+          pk[e] = pack2(__float_as_uint(p0), __float_as_uint(p1));
+        }
+        tmem_st_16(tmem_s + st * AT_BN + part * (AT_PART / 2) + lane_base, pk);
+        tmem_wait_st();
+      } else {
       float mx = -INFINITY;
       if (j * AT_BN + AT_BN - 1 > pos_first) {  // the diagonal: keys beyond this row's position are hidden
 #pragma unroll
@@ -342,6 +367,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       tmem_st_16(tmem_s + st * AT_BN + part * (AT_PART / 2) + lane_base, pk);
       tmem_wait_st();
       l += sum;
+      }  // softmax
       // keys past the end of the sequence in the last tile: their V rows were not loaded; zero them
       if (j * AT_BN + AT_BN > len) {
         ok = ok && mbar_wait(v_full + st, ((uint32_t)j >> 1) & 1, &abort_flag);
@@ -358,6 +384,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
+      // SIGMOID never waits for a P V inside the loop to rescale; it follows them one tile behind here, where the
+      // product has had a whole tile's time to finish, so that the wait after the loop cannot mistake an earlier
+      // phase of the same parity for the last one
+      if (SIGMOID && j > 0) ok = ok && mbar_wait(pv_done, (j - 1) & 1, &abort_flag);
     }
     if (!ok && lane == 0) {
       abort_flag = 1;
@@ -373,7 +403,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       float total = 0.f;
 #pragma unroll
       for (int o = 0; o < AT_PARTS; ++o) total += xchg[o * AT_BM + rr];
-      const float inv = total > 0.f ? 1.0f / total : 0.f;
+      float inv = total > 0.f ? 1.0f / total : 0.f;
+      if (SIGMOID) inv = (gate && valid_row) ? gate[(size_t)(qs + R / g) * Hq + hk * g + R % g] : 1.f;
       // The output tile goes through shared memory (where the query tile was: every product that read
       // it has finished), so that it leaves in whole rows instead of one 64-byte piece per thread.
       // Chunk c of row r sits at chunk position c ^ (r % CH) of its row, which spreads a warp's rows
@@ -423,14 +454,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #undef abort_flag
 }
 
-template <int D>
+template <int D, bool SIGMOID = false>
 static int attn_tc_launch(const void* q, const void* k_pages, const void* v_pages, void* out, const int* q_start,
                           const int* kv_len, const int* block_table, int table_stride, int page_size, int num_pages,
-                          int B, int max_q_len, int Hq, int Hkv, float scale, int* status, cudaStream_t stream) {
+                          int B, int max_q_len, int Hq, int Hkv, float scale, int* status, cudaStream_t stream,
+                          const float* head_bias = nullptr, const float* gate = nullptr) {
   using S = AttnTcShape<D>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<D, SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)S::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -444,9 +477,9 @@ static int attn_tc_launch(const void* q, const void* k_pages, const void* v_page
   const long long tiles = ((long long)max_q_len * g + AT_BM - 1) / AT_BM;
   if (tiles > 65535) return Q3_ERR_SIZE;
   dim3 grid(Hkv, (unsigned)tiles, B);
-  q3::launch(attn_tc_kernel<D>, grid, dim3(AT_THREADS), S::SMEM_BYTES, stream, map_k, map_v, (const __nv_bfloat16*)q,
-             (__nv_bfloat16*)out, q_start, kv_len, block_table, table_stride, page_size, num_pages, Hq, Hkv,
-             scale * 1.4426950408889634f, status);
+  q3::launch(attn_tc_kernel<D, SIGMOID>, grid, dim3(AT_THREADS), S::SMEM_BYTES, stream, map_k, map_v,
+             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, q_start, kv_len, block_table, table_stride, page_size, num_pages,
+             Hq, Hkv, scale * 1.4426950408889634f, status, head_bias, gate);
   return launch_status();
 }
 
@@ -472,4 +505,23 @@ extern "C" int q3_attn_tc(const void* q, const void* k_pages, const void* v_page
                                   num_pages, B, max_q_len, Hq, Hkv, scale, status, stream);
   return q3::attn_tc_launch<128>(q, k_pages, v_pages, out, q_start, kv_len, block_table, table_stride, page_size,
                                  num_pages, B, max_q_len, Hq, Hkv, scale, status, stream);
+}
+
+// The same kernel with sigmoid weights (see attn_sigmoid.cu): head_bias float32 [Hq] or null, gate float32
+// [T, Hq] or null; the other arguments and the sizes taken as q3_attn_tc.
+extern "C" int q3_attn_sigmoid_tc(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                  const float* head_bias, const float* gate, const int* q_start, const int* kv_len,
+                                  const int* block_table, int table_stride, int page_size, int num_pages, int B,
+                                  int max_q_len, int Hq, int Hkv, int D, float scale, int* status, cudaStream_t stream) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv || (D != 64 && D != 128) || table_stride <= 0 || B > 65535 || Hkv > 65535 ||
+      (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64))
+    return Q3_ERR_SIZE;
+  if ((uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16 || (uintptr_t)out % 16)
+    return Q3_ERR_ALIGN;
+  if (D == 64)
+    return q3::attn_tc_launch<64, true>(q, k_pages, v_pages, out, q_start, kv_len, block_table, table_stride, page_size,
+                                        num_pages, B, max_q_len, Hq, Hkv, scale, status, stream, head_bias, gate);
+  return q3::attn_tc_launch<128, true>(q, k_pages, v_pages, out, q_start, kv_len, block_table, table_stride, page_size,
+                                       num_pages, B, max_q_len, Hq, Hkv, scale, status, stream, head_bias, gate);
 }

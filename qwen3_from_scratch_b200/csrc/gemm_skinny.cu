@@ -68,6 +68,7 @@ struct SkinnyFuse {
   const float* next_w;  // EPI 2, optional: weight [N] of the norm that comes next, and
   __nv_bfloat16* scaled_out;  // [T, N]: the new rows times that weight, the operand of a NORMED product
   int early;            // EPI 2: the stream may be read ahead of the wait (the launch before did not write it)
+  int gate_act;         // EPI 1: the gate's activation, a Q3_ACT_* code (0: SiLU)
 };
 
 constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
@@ -267,7 +268,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         gate *= rs_s[tok];
         up *= rs_s[tok];
       }
-      out[(size_t)tok * ldo + (row0 >> 1) + f] = from_float<OutT>(up * (gate / (1.0f + expf(-gate))));
+      out[(size_t)tok * ldo + (row0 >> 1) + f] = from_float<OutT>(up * activate(gate, fuse.gate_act));
     }
   }
 }
@@ -322,16 +323,19 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
 
 // out[T, N] (row pitch ldo) = X[T, K] * W[N, K]^T for T <= 16; X, W bfloat16, K a multiple of 8.
 // out_f32 != 0: float32 output, else bfloat16.  swiglu != 0: W's rows alternate gate/up in blocks of
-// eight, N is a multiple of 16 and out is [T, N / 2].
+// eight, N is a multiple of 16 and out is [T, N / 2]; the gate's activation is Q3_ACT code swiglu - 1.
 extern "C" int q3_gemm_skinny(const void* X, const void* W, void* out, int T, int N, int K, int ldo, int out_f32,
                               int swiglu, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (T > 16 || K <= 0 || K % 8 || (swiglu && (N % 16 || out_f32))) return Q3_ERR_SIZE;
+  if (T > 16 || K <= 0 || K % 8 || swiglu < 0 || swiglu > 1 + Q3_ACT_GELU_TANH || (swiglu && (N % 16 || out_f32)))
+    return Q3_ERR_SIZE;
   if ((uintptr_t)X % 16 || (uintptr_t)W % 16) return Q3_ERR_ALIGN;
   using bf16 = __nv_bfloat16;
   if (swiglu) {
-    if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16>(X, W, out, T, N, K, ldo, stream);
-    return q3::gemm_skinny_launch<2, 1, bf16>(X, W, out, T, N, K, ldo, stream);
+    q3::SkinnyFuse fuse{};
+    fuse.gate_act = swiglu - 1;
+    if (T <= 8) return q3::gemm_skinny_launch<1, 1, bf16>(X, W, out, T, N, K, ldo, stream, fuse);
+    return q3::gemm_skinny_launch<2, 1, bf16>(X, W, out, T, N, K, ldo, stream, fuse);
   }
   if (out_f32) {
     if (T <= 8) return q3::gemm_skinny_launch<1, 0, float>(X, W, out, T, N, K, ldo, stream);

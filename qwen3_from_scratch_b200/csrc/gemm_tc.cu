@@ -44,7 +44,7 @@ template <int EPI>
 struct TcThreads {
   // the SwiGLU epilogue too has two warps per quarter of the rows (they take every second piece of 32 columns): with
   // one warp per scheduler a tile's epilogue is a single chain of latencies, which the last tile of a block shows
-  static constexpr int EPI_WARPS = EPI == 2 ? TC_QKV_EPI_WARPS : (EPI == 1 ? 8 : 4);
+  static constexpr int EPI_WARPS = EPI == 2 ? TC_QKV_EPI_WARPS : ((EPI == 1 || EPI == 3) ? 8 : 4);
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
@@ -301,7 +301,7 @@ __device__ __forceinline__ void qkv_tile_epilogue(uint32_t tmem_acc, unsigned ch
 }
 
 // Stores 32 consecutive columns of one row.  EPI 0: as they are.  EPI 1: SwiGLU on column blocks
-// (gate 8, up 8, ...), 16 outputs at half the column index.
+// (gate 8, up 8, ...), 16 outputs at half the column index.  EPI 3: the same with a ReLU gate.
 template <int EPI, typename OutT>
 __device__ __forceinline__ void tc_store_chunk(const uint32_t (&v)[32], OutT* __restrict__ C, int row, int col0, int N,
                                                int ldc) {
@@ -340,7 +340,7 @@ __device__ __forceinline__ void tc_store_chunk(const uint32_t (&v)[32], OutT* __
         const float gate = __uint_as_float(v[16 * j + i]), up = __uint_as_float(v[16 * j + 8 + i]);
         // silu by the fast exponential and division: their error (about 2^-21) is far below the
         // bfloat16 rounding of the result, and the exact forms made this epilogue longer than the main loop
-        r[8 * j + i] = up * __fdividef(gate, 1.0f + __expf(-gate));
+        r[8 * j + i] = EPI == 3 ? up * fmaxf(gate, 0.f) : up * __fdividef(gate, 1.0f + __expf(-gate));
       }
     if (col0 + 32 <= N && ((uintptr_t)dst & 15) == 0 && sizeof(OutT) == 2) {
 #pragma unroll
@@ -362,7 +362,8 @@ __device__ __forceinline__ void tc_store_chunk(const uint32_t (&v)[32], OutT* __
   }
 }
 
-// EPI 0: store.  EPI 1: SwiGLU.  EPI 2: the QKV epilogue with heads of HD values (C is not written).
+// EPI 0: store.  EPI 1: SwiGLU.  EPI 2: the QKV epilogue with heads of HD values (C is not written).  EPI 3: gated
+// like EPI 1, the gate a ReLU.
 template <int BN, int EPI, typename OutT, int HD = 128>
 __global__ void __launch_bounds__(TcThreads<EPI>::THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -841,13 +842,15 @@ static int gemm_tc_dispatch(const void* A, const void* W, void* C, int M, int N,
 
 // C[M, N] (row pitch ldc) = A[M, K] * W[N, K]^T; A, W bfloat16 with 16-byte aligned bases and K a multiple
 // of 8 (TMA wants row pitches in multiples of 16 bytes).  out_f32: float32 output, else bfloat16.
-// swiglu: W's rows alternate gate/up in blocks of eight, N a multiple of 16, C is [M, N / 2] bfloat16.
+// swiglu: W's rows alternate gate/up in blocks of eight, N a multiple of 16, C is [M, N / 2] bfloat16: 1 for the
+// SiLU gate, 2 for a ReLU gate.
 extern "C" int q3_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int out_f32,
                           int swiglu, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || (swiglu && (N % 16 || out_f32))) return Q3_ERR_SIZE;
+  if (K <= 0 || K % 8 || swiglu < 0 || swiglu > 2 || (swiglu && (N % 16 || out_f32))) return Q3_ERR_SIZE;
   if ((uintptr_t)A % 16 || (uintptr_t)W % 16) return Q3_ERR_ALIGN;
   using bf16 = __nv_bfloat16;
+  if (swiglu == 2) return q3::gemm_tc_dispatch<3, bf16>(A, W, C, M, N, K, ldc, status, stream);
   if (swiglu) return q3::gemm_tc_dispatch<1, bf16>(A, W, C, M, N, K, ldc, status, stream);
   if (out_f32) return q3::gemm_tc_dispatch<0, float>(A, W, C, M, N, K, ldc, status, stream);
   return q3::gemm_tc_dispatch<0, bf16>(A, W, C, M, N, K, ldc, status, stream);
@@ -858,9 +861,10 @@ extern "C" int q3_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
 extern "C" int q3_gemm_tc_pair(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int out_f32,
                                int swiglu, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || (swiglu && (N % 16 || out_f32))) return Q3_ERR_SIZE;
+  if (K <= 0 || K % 8 || swiglu < 0 || swiglu > 2 || (swiglu && (N % 16 || out_f32))) return Q3_ERR_SIZE;
   if ((uintptr_t)A % 16 || (uintptr_t)W % 16) return Q3_ERR_ALIGN;
   using bf16 = __nv_bfloat16;
+  if (swiglu == 2) return q3::gemm_tc_pair_launch<3, bf16>(A, W, C, M, N, K, ldc, status, stream);
   if (swiglu) return q3::gemm_tc_pair_launch<1, bf16>(A, W, C, M, N, K, ldc, status, stream);
   if (out_f32) return q3::gemm_tc_pair_launch<0, float>(A, W, C, M, N, K, ldc, status, stream);
   return q3::gemm_tc_pair_launch<0, bf16>(A, W, C, M, N, K, ldc, status, stream);

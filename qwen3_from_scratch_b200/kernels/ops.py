@@ -105,6 +105,9 @@ _SIGNATURES = {
     "q3_qk_gate_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                         _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
+    "q3_attn_sigmoid_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                           _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                           _c_void_p, _c_void_p],
     "q3_attn_sigmoid_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                             _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -451,9 +454,10 @@ def gemm_skinny_takes(rows: int, weight: torch.Tensor) -> bool:
     return rows <= SKINNY_MAX_ROWS and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0
 
 
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu_blocks: bool = False) -> None:
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu_blocks: bool = False,
+                activation: str = "silu") -> None:
     """out[T, N] = x[T, K] @ w[N, K]^T for T <= 16, bfloat16 in, out bfloat16 or float32.
-    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [T, N / 2]."""
+    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [T, N / 2] = up * act(gate)."""
     _check("gemm_skinny.x", x, torch.bfloat16)
     _check("gemm_skinny.w", w, torch.bfloat16)
     _check("gemm_skinny.out", out)
@@ -463,7 +467,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu_bloc
     if w.shape[1] != K or tuple(out.shape) != (T, want_cols) or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_skinny: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
     code = library().q3_gemm_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols,
-                                    1 if out.dtype == torch.float32 else 0, 1 if swiglu_blocks else 0, _stream())
+                                    1 if out.dtype == torch.float32 else 0,
+                                    1 + activation_code(activation, gate=True) if swiglu_blocks else 0, _stream())
     _done("gemm_skinny", code, f"T {T} N {N} K {K}")
 
 
@@ -610,10 +615,14 @@ def gemm_tc_swiglu_pays(rows: int, weight: torch.Tensor) -> Optional[str]:
     return "single" if narrow and rows >= 128 else None
 
 
+GEMM_TC_GATES = {"silu": 1, "relu": 2}  # the gates that the tcgen05 product's epilogue applies
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
-            swiglu_blocks: bool = False, pair: bool = False) -> None:
+            swiglu_blocks: bool = False, pair: bool = False, activation: str = "silu") -> None:
     """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in TMEM).
-    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [M, N / 2].
+    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [M, N / 2] = up * act(gate),
+    ``activation`` one of ``GEMM_TC_GATES``.
     ``pair``: by pairs of CTAs on 256 x 256 tiles (the paired instruction) instead of single CTAs."""
     _check("gemm_tc.x", x, torch.bfloat16)
     _check("gemm_tc.w", w, torch.bfloat16)
@@ -625,7 +634,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.T
         raise KernelError(f"gemm_tc: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
     entry = library().q3_gemm_tc_pair if pair else library().q3_gemm_tc
     code = entry(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, want_cols,
-                 1 if out.dtype == torch.float32 else 0, 1 if swiglu_blocks else 0, status.data_ptr(), _stream())
+                 1 if out.dtype == torch.float32 else 0, GEMM_TC_GATES[activation] if swiglu_blocks else 0,
+                 status.data_ptr(), _stream())
     _done("gemm_tc", code, f"M {M} N {N} K {K}{' pair' if pair else ''}")
 
 
@@ -1203,6 +1213,28 @@ def attn_sigmoid_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     _done("attn_sigmoid_mma", code, f"heads {Hq}/{Hkv}, head_dim {D}")
 
 
+def attn_sigmoid_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                    head_bias: Optional[torch.Tensor], gate: Optional[torch.Tensor], q_start: torch.Tensor,
+                    kv_len: torch.Tensor, block_table: torch.Tensor, num_seqs: int, max_q_len: int, scale: float,
+                    status: torch.Tensor) -> None:
+    """Portions with sigmoid weights on the tcgen05 tensor cores (the kernel of ``attn_tc`` with the softmax
+    taken out): head size 64 or 128, pages of 8 to 64 tokens."""
+    T, Hq, D, num_pages, Hkv, page_size = _attn_common("attn_sigmoid_tc", q, k_pages, v_pages, out, q_start, kv_len,
+                                                        block_table)
+    if q_start.numel() < num_seqs + 1 or kv_len.numel() < num_seqs or block_table.shape[0] < num_seqs:
+        raise KernelError(f"attn_sigmoid_tc: {num_seqs} sequences, q_start {q_start.numel()}, kv_len {kv_len.numel()}")
+    for name, t, n in (("head_bias", head_bias, Hq), ("gate", gate, T * Hq)):
+        if t is not None:
+            _check(f"attn_sigmoid_tc.{name}", t, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"attn_sigmoid_tc: {name} has {t.numel()} values, {n} expected")
+    code = library().q3_attn_sigmoid_tc(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                        _ptr(head_bias), _ptr(gate), q_start.data_ptr(), kv_len.data_ptr(),
+                                        block_table.data_ptr(), block_table.shape[1], page_size, num_pages, num_seqs,
+                                        int(max_q_len), Hq, Hkv, D, float(scale), status.data_ptr(), _stream())
+    _done("attn_sigmoid_tc", code, f"heads {Hq}/{Hkv}, head_dim {D}, page {page_size}")
+
+
 def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                       head_bias: Optional[torch.Tensor], gate: Optional[torch.Tensor], q_start: torch.Tensor,
                       kv_len: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, num_seqs: int,
@@ -1210,7 +1242,8 @@ def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       partial: Optional[torch.Tensor] = None, kernel: str = "auto") -> None:
     """Causal attention with sigmoid weights of a mixed batch over the pages (see ``attn_sigmoid``): rows
     [0, num_decode) bring one token each and go to the decode form of the tensor-core kernel, the rest to its
-    portion form; float32, shapes it refuses and ``kernel="plain"`` go to the plain kernel."""
+    portion form, or for heads of 64 or 128 and pages of 8 to 64 tokens to the tcgen05 kernel (``kernel="mma"``
+    keeps them on mma.sync); float32, shapes it refuses and ``kernel="plain"`` go to the plain kernel."""
     T, Hq, D = q.shape
     Hkv = k_pages.shape[1]
     if block_table.dim() != 2 or max_kv_len > block_table.shape[1] * k_pages.shape[2]:
@@ -1227,5 +1260,8 @@ def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         attn_sigmoid_mma(q, k_pages, v_pages, out, head_bias, gate, q_start, kv_len, block_table, decode, 1, scale,
                          status, decode=True, num_splits=splits, partial=partial)
     if num_seqs > decode:
-        attn_sigmoid_mma(q, k_pages, v_pages, out, head_bias, gate, q_start[decode:], kv_len[decode:],
-                         block_table[decode:], num_seqs - decode, max_q_len, scale, status)
+        rest = (q_start[decode:], kv_len[decode:], block_table[decode:], num_seqs - decode, max_q_len, scale, status)
+        if kernel != "mma" and max_q_len > 1 and attn_tc_takes(D, k_pages.shape[2], 0):
+            attn_sigmoid_tc(q, k_pages, v_pages, out, head_bias, gate, *rest)
+        else:
+            attn_sigmoid_mma(q, k_pages, v_pages, out, head_bias, gate, *rest)

@@ -58,13 +58,15 @@ class GatedMLP(FeedForward):
         self.gate_up = Linear(merged, rt, tag="ffn.gate_up")
         self.down = Linear(weights.pop(self.tensors["down"]), rt, tag="ffn.down")
         self._act = rt.shared("ffn.act", rt.max_tokens, self.intermediate_size)
-        # the products that apply the gate in their epilogue are built for the SiLU gate
-        self.fused_gate = self.blocks_of_eight and self.activation == "silu"
+        # the few-rows product applies any gate in its epilogue, the tcgen05 product those of ops.GEMM_TC_GATES; the
+        # product that also applies a norm that was never computed is built for the SiLU gate
+        self.fused_gate = self.blocks_of_eight
 
     fuses_stream = True
 
     def can_fuse_stream(self, rows: int) -> bool:
-        return self.fused_gate and self.gate_up.takes_stream_norm(rows) and self.down.can_add_into_stream(rows)
+        return (self.fused_gate and self.activation == "silu" and self.gate_up.takes_stream_norm(rows)
+                and self.down.can_add_into_stream(rows))
 
     def forward(self, x, into_stream=None, next_norm_weight=None):
         act = self._act[: x.shape[0]]
@@ -74,13 +76,13 @@ class GatedMLP(FeedForward):
             ops.gemm_skinny_normed(x.scaled, x.sumsq, x.parts, x.eps, self.gate_up.weight, act, swiglu_blocks=True)
         elif self.fused_gate and ops.gemm_skinny_takes(rows, self.gate_up.weight):
             # decoding: stream the weight once, activation applied before the store
-            ops.gemm_skinny(x, self.gate_up.weight, act, swiglu_blocks=True)
-        elif (self.fused_gate and ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight)
-              and ops.gemm_tc_takes(x, self.gate_up.weight)):
+            ops.gemm_skinny(x, self.gate_up.weight, act, swiglu_blocks=True, activation=self.activation)
+        elif (self.fused_gate and self.activation in ops.GEMM_TC_GATES
+              and ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight) and ops.gemm_tc_takes(x, self.gate_up.weight)):
             # prompt portions: the engine's tcgen05 product with the activation in its epilogue, so the
             # [T, 2I] gate/up product never goes to memory
             ops.gemm_tc(x, self.gate_up.weight, act, self.rt.status, swiglu_blocks=True,
-                        pair=ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight) == "pair")
+                        pair=ops.gemm_tc_swiglu_pays(rows, self.gate_up.weight) == "pair", activation=self.activation)
         else:
             ops.gated_act(self.gate_up(x), act, interleave8=self.blocks_of_eight, activation=self.activation)
         if into_stream is not None:

@@ -210,6 +210,21 @@ def test_post_norm_block_with_shift_and_relu_gate(dtype):
         close(torch.cat(got), want, dtype, f"block {cuts}")
 
 
+@pytest.mark.parametrize("rows", [3, 12, 40, 200, 1100])
+def test_relu_gated_feed_forward_in_every_product(rows):
+    """bfloat16: the gate is applied by the few-rows product (up to 16 rows), by the tcgen05 product's epilogue
+    (single CTAs from 128 rows, pairs from 1,024) or by the gate kernel after the library's product."""
+    from qwen3_from_scratch_b200.parts.base import PartSpec, Runtime
+    from qwen3_from_scratch_b200.registry import create_part
+    part = create_part("feed_forward", PartSpec("gated_mlp", {
+        "hidden_size": 128, "intermediate_size": 256, "activation": "relu",
+        "names": {"gate": "gate", "up": "up", "down": "down"}}), name="f")
+    dev, ref = part_weights(part, "bfloat16", 23)
+    part.setup(Runtime(torch.device("cuda:0"), torch.bfloat16, 2048, 2), dev)
+    x = torch.randn(rows, 128, generator=torch.Generator().manual_seed(rows)).to(torch.bfloat16)
+    close(part.forward(x.cuda()), plain.relu_glu(x.double(), ref, ""), "bfloat16", f"{rows} rows")
+
+
 def test_shift_state_is_the_input_before_the_shift():
     """mu = 1 makes the mixer read the previous token's x alone: the second token of a request, fed alone, must
     see the first one's stream, not the first one's shifted input."""
@@ -272,7 +287,8 @@ def test_one_far_key_decides_the_output(dtype):
 
 
 # ---------------------------------------------------------------------- the tensor-core kernel against the plain one
-@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 4), (6, 1, 48, 16), (8, 2, 64, 16), (8, 1, 128, 16), (16, 1, 256, 8)])
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 4), (6, 1, 48, 16), (8, 2, 64, 16), (8, 1, 128, 16), (4, 4, 128, 8),
+                                           (6, 2, 64, 32), (16, 1, 256, 8)])
 def test_tensor_core_sigmoid_attention_equals_the_plain_kernel(hq, hkv, d, page):
     """A mixed batch: three single tokens at contexts that end just before, at and just after a tile's and a page's
     edge, and two portions (one from position 0, one continuing); key ranges of the decode form from 1 to many."""
@@ -302,13 +318,15 @@ def test_tensor_core_sigmoid_attention_equals_the_plain_kernel(hq, hkv, d, page)
     want = torch.empty_like(q)
     ops.sigmoid_attention(*args, want, *rest, kernel="plain")
     scale = float(want.float().abs().max())
-    for partial_floats in (0, 3 * 2 * hq * d, ops.sigmoid_partial_numel(3, hq, d)):
+    # the portions on mma.sync with 0, 2 and as many key ranges of the decode form as it likes, then on tcgen05
+    for partial_floats, kernel in ((0, "mma"), (3 * 2 * hq * d, "mma"), (ops.sigmoid_partial_numel(3, hq, d), "mma"),
+                                   (ops.sigmoid_partial_numel(3, hq, d), "auto")):
         partial = torch.empty(partial_floats, device="cuda") if partial_floats else None
         got = torch.full_like(q, float("nan"))
-        ops.sigmoid_attention(*args, got, *rest, partial=partial)
+        ops.sigmoid_attention(*args, got, *rest, partial=partial, kernel=kernel)
         assert int(status.item()) == 0
-        # both round the weights' sum to bfloat16 once; the tensor-core kernel also rounds each weight
-        assert float((got.float() - want.float()).abs().max()) <= 1.5e-2 * scale, partial_floats
+        # both round the weights' sum to bfloat16 once; the tensor-core kernels also round each weight
+        assert float((got.float() - want.float()).abs().max()) <= 1.5e-2 * scale, (partial_floats, kernel)
 
 
 # ---------------------------------------------------------------------- whole models
