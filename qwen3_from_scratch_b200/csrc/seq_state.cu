@@ -19,9 +19,55 @@
 
 namespace q3 {
 
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 // ---------------------------------------------------------------- token shift
 // One block per token.  The block of a request's first token of the step reads the state (the x of the
 // token before) and, element by element after reading it, stores the portion's last x there.
+// Four features per thread with 16-byte loads (W a multiple of 4, rows 16-byte aligned); otherwise as below.
+template <typename T>
+__global__ void token_shift_vec4_kernel(const float* __restrict__ x, const float* __restrict__ mu, float* __restrict__ state,
+                                        const int* __restrict__ q_start, const int* __restrict__ tok_seq,
+                                        const int* __restrict__ slot_ids, T* __restrict__ out, int W, int num_slots,
+                                        int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int b = tok_seq[t];
+  const int slot = slot_ids[b];
+  const bool live = slot >= 0 && slot < num_slots;
+  if (!live && threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+  const bool first = t == q_start[b];
+  const float* cur = x + (size_t)t * W;
+  const float* prev = first ? (live ? state + (size_t)slot * W : nullptr) : cur - W;
+  const float* last = x + (size_t)(q_start[b + 1] - 1) * W;
+  T* o = out + (size_t)t * W;
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    const float4 c = *reinterpret_cast<const float4*>(cur + i);
+    const float4 m = *reinterpret_cast<const float4*>(mu + i);
+    const float4 p = prev ? *reinterpret_cast<const float4*>(prev + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float r[4] = {c.x + (p.x - c.x) * m.x, c.y + (p.y - c.y) * m.y, c.z + (p.z - c.z) * m.z, c.w + (p.w - c.w) * m.w};
+    if (!live) {
+      for (int k = 0; k < 4; ++k) o[i + k] = from_float<T>(0.f);
+      continue;
+    }
+    if (sizeof(T) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(o + i) = pk;
+    } else {
+      *reinterpret_cast<float4*>(o + i) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+    // the element's old state has been read by this thread and by nobody else: it may be renewed now
+    if (first) *reinterpret_cast<float4*>(state + (size_t)slot * W + i) = *reinterpret_cast<const float4*>(last + i);
+  }
+}
+
 template <typename T>
 __global__ void token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mu, float* __restrict__ state,
                                    const int* __restrict__ q_start, const int* __restrict__ tok_seq,
@@ -97,12 +143,101 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int ldx, const float
   out[(size_t)t * C + c] = from_float<T>(activate(acc, act));
 }
 
+// bfloat16, C a multiple of 8, K up to CONV_KMAX: a thread takes eight channels (16-byte loads and stores) and a run
+// of CONV_RUN tokens, keeps the taps and the window of the last K - 1 inputs in registers and slides the window from
+// token to token; at a request's first token of the step the window is refilled from the state.  The state is
+// only read here, also for a portion of one token (conv_state_kernel renews every request's afterwards).
+constexpr int CONV_KMAX = 4, CONV_RUN = 16;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    f[2 * k] = __uint_as_float(w[k] << 16);
+    f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+  }
+}
+
+__global__ void causal_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ in_bias,
+                                          const float* __restrict__ w, const float* __restrict__ bias,
+                                          const float* __restrict__ state, const int* __restrict__ q_start,
+                                          const int* __restrict__ tok_seq, const int* __restrict__ slot_ids,
+                                          __nv_bfloat16* __restrict__ out, int Ttot, int C, int K, int act, int num_slots,
+                                          int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int t0 = blockIdx.x * CONV_RUN, t1 = min(Ttot, t0 + CONV_RUN);
+  float taps[CONV_KMAX][8], ib[8], cb[8], win[CONV_KMAX - 1][8];  // win[0] the oldest of the K - 1 inputs before the token
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    ib[e] = in_bias ? in_bias[c + e] : 0.f;
+    cb[e] = bias ? bias[c + e] : 0.f;
+#pragma unroll
+    for (int j = 0; j < CONV_KMAX; ++j) taps[j][e] = j < K ? w[(size_t)(c + e) * K + j] : 0.f;
+  }
+  // entry i of the window before token t, place `at` in its portion: the input `K - 1 - i` tokens back
+  auto fill = [&](int t, int at, int slot) {
+#pragma unroll
+    for (int i = 0; i < CONV_KMAX - 1; ++i) {
+      if (i >= K - 1) break;
+      const int back = K - 1 - i;
+      if (at - back >= 0) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(x + (size_t)(t - back) * ldx + c), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[i][e] = f[e] + ib[e];
+      } else {
+        const float* st = state + ((size_t)slot * (K - 1) + (K - 1 + at - back)) * C + c;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[i][e] = slot >= 0 ? st[e] : 0.f;
+      }
+    }
+  };
+  for (int t = t0; t < t1; ++t) {
+    const int b = tok_seq[t];
+    const int at = t - q_start[b];
+    if (t == t0 || at == 0) {
+      int slot = slot_ids[b];
+      if (slot < 0 || slot >= num_slots) {
+        if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+        slot = -1;
+      }
+      fill(t, at, slot);
+    }
+    float v[8], acc[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + (size_t)t * ldx + c), v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      v[e] += ib[e];
+      acc[e] = cb[e];
+#pragma unroll
+      for (int i = 0; i < CONV_KMAX - 1; ++i)
+        if (i < K - 1) acc[e] = fmaf(taps[i][e], win[i][e], acc[e]);
+      acc[e] = activate(fmaf(taps[K - 1][e], v[e], acc[e]), act);
+    }
+    uint4 pk;
+    pk.x = pack_pair(acc[0], acc[1]);
+    pk.y = pack_pair(acc[2], acc[3]);
+    pk.z = pack_pair(acc[4], acc[5]);
+    pk.w = pack_pair(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * C + c) = pk;
+#pragma unroll
+    for (int i = 0; i < CONV_KMAX - 1; ++i) {
+      if (i >= K - 1) break;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) win[i][e] = (i + 1 < K - 1) ? win[i + 1 < CONV_KMAX - 1 ? i + 1 : i][e] : v[e];
+    }
+  }
+}
+
 // grid (requests, channel chunks): the last K - 1 inputs of each request, from the portion and, where the
 // portion is shorter than that, from the old state (moved up in place, oldest first).
 template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ in_bias,
                                   float* __restrict__ state, const int* __restrict__ q_start,
-                                  const int* __restrict__ slot_ids, int C, int K, int num_slots) {
+                                  const int* __restrict__ slot_ids, int C, int K, int num_slots, int singles_too) {
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x;
@@ -110,7 +245,7 @@ __global__ void conv_state_kernel(const T* __restrict__ x, int ldx, const float*
   const int slot = slot_ids[b];
   if (c >= C || slot < 0 || slot >= num_slots) return;
   const int t0 = q_start[b], n = q_start[b + 1] - t0;
-  if (n == 1) return;  // the convolution kernel has moved a single token's tail itself
+  if (n == 1 && !singles_too) return;  // the plain convolution kernel has moved a single token's tail itself
   const float ib = in_bias ? in_bias[c] : 0.f;
   float* st = state + (size_t)slot * (K - 1) * C + c;
   for (int i = 0; i < K - 1; ++i) {
@@ -199,6 +334,47 @@ __global__ void rglru_scan_kernel(const T* __restrict__ proj, int ld_proj, int y
   state[(size_t)slot * C + c] = S;
 }
 
+// A token's N values of B (or C) into registers, four at a time where N and the row allow 16-byte loads.
+template <int NMAX>
+__device__ __forceinline__ void load_row(const float* __restrict__ row, int N, float (&v)[NMAX]) {
+  if (NMAX >= 4 && N % 4 == 0 && ((uintptr_t)row & 15) == 0) {
+#pragma unroll
+    for (int n4 = 0; n4 < NMAX / 4; ++n4) {
+      if (4 * n4 < N) {
+        const float4 f = reinterpret_cast<const float4*>(row)[n4];
+        v[4 * n4] = f.x; v[4 * n4 + 1] = f.y; v[4 * n4 + 2] = f.z; v[4 * n4 + 3] = f.w;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n)
+      if (n < N) v[n] = row[n];
+  }
+}
+
+// exp(step * A) with A = -exp(A_log): the float32 run evaluates it as written; the bfloat16 run keeps A in units of
+// the base-2 exponential and takes exp2f, a shorter sequence whose error (2 ulp) is far below that run's roundings.
+template <typename T> __device__ __forceinline__ float decay_rate(float a_log) {
+  return sizeof(T) == 4 ? -expf(a_log) : -expf(a_log) * 1.4426950408889634f;
+}
+template <typename T> __device__ __forceinline__ float decay(float step, float rate) {
+  if (sizeof(T) == 4) return expf(step * rate);
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(step * rate));
+  return y;
+}
+// softplus and SiLU of the scans: as written in the float32 run; in the bfloat16 run by the hardware's base-2
+// exponential, logarithm and reciprocal (relative error about 2^-21, still float32 arithmetic), because the special
+// function unit, which also serves the library forms' slow paths, is what bounds these kernels.
+template <typename T> __device__ __forceinline__ float scan_softplus(float x) {
+  if (sizeof(T) == 4) return softplus_f(x);
+  return fmaxf(x, 0.f) + __logf(1.0f + __expf(-fabsf(x)));
+}
+template <typename T> __device__ __forceinline__ float scan_silu(float z) {
+  if (sizeof(T) == 4) return silu_f(z);
+  return z * __fdividef(1.0f, 1.0f + __expf(-z));
+}
+
 // ---------------------------------------------------------------- selective scan (Mamba)
 // grid (requests, channel chunks), one thread per channel with its N state values in registers.
 // xc: [T, I] (after convolution and activation); proj: [T, ld_proj] with z at column z_col; bc: float32
@@ -226,27 +402,28 @@ __global__ void selective_scan_kernel(const T* __restrict__ xc, const T* __restr
   float* st = state + (size_t)slot * N * I + c;
 #pragma unroll
   for (int n = 0; n < NMAX; ++n) {
-    A[n] = n < N ? -expf(A_log[(size_t)c * N + n]) : 0.f;
+    A[n] = n < N ? decay_rate<T>(A_log[(size_t)c * N + n]) : 0.f;
     S[n] = n < N ? st[(size_t)n * I] : 0.f;
   }
   const float db = dt_bias[c], dskip = Dp[c];
   for (int t = t0; t < t1; ++t) {
-    const float step = softplus_f(dt[(size_t)t * I + c] + db);
+    const float step = scan_softplus<T>(dt[(size_t)t * I + c] + db);
     const float x = to_float(xc[(size_t)t * I + c]);
     const float sx = step * x;
-    const float* Bt = bc + (size_t)t * 2 * N;
-    const float* Ct = Bt + N;
+    float Bt[NMAX], Ct[NMAX];
+    load_row<NMAX>(bc + (size_t)t * 2 * N, N, Bt);
+    load_row<NMAX>(bc + (size_t)t * 2 * N + N, N, Ct);
     float y = 0.f;
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) {
       if (n < N) {
-        S[n] = fmaf(expf(step * A[n]), S[n], sx * Bt[n]);
+        S[n] = fmaf(decay<T>(step, A[n]), S[n], sx * Bt[n]);
         y = fmaf(S[n], Ct[n], y);
       }
     }
     y = fmaf(dskip, x, y);
     const float z = to_float(proj[(size_t)t * ld_proj + z_col + c]);
-    out[(size_t)t * I + c] = from_float<T>(y * silu_f(z));
+    out[(size_t)t * I + c] = from_float<T>(y * scan_silu<T>(z));
   }
 #pragma unroll
   for (int n = 0; n < NMAX; ++n)
@@ -326,10 +503,19 @@ __global__ void rglru_carry_kernel(float* __restrict__ scratch, float* __restric
   const int chunks = (n + SCAN_CHUNK - 1) / SCAN_CHUNK;
   float* sc = scratch + ((size_t)(q_start[b] / SCAN_CHUNK + b) * 2) * C + c;
   float S = live ? state[(size_t)slot * C + c] : 0.f;
-  for (int j = 0; j < chunks; ++j, sc += 2 * (size_t)C) {
-    const float P = sc[0], V = sc[C];
-    sc[0] = S;
-    S = fmaf(P, S, V);
+  for (int j0 = 0; j0 < chunks; j0 += 8) {  // eight records are asked for together, then walked
+    float P[8], V[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const bool in = j0 + k < chunks;
+      P[k] = in ? sc[(size_t)(j0 + k) * 2 * C] : 1.f;
+      V[k] = in ? sc[(size_t)(j0 + k) * 2 * C + C] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (j0 + k < chunks) sc[(size_t)(j0 + k) * 2 * C] = S;
+      S = fmaf(P[k], S, V[k]);
+    }
   }
   if (live) state[(size_t)slot * C + c] = S;
 }
@@ -337,8 +523,10 @@ __global__ void rglru_carry_kernel(float* __restrict__ scratch, float* __restric
 // Selective scan by chunks.  scratch [chunk][N + 1][I]: PASS 1 leaves the zero-start state per n and, at n = N, the
 // chunk's sum of step sizes (the chunk's product of exp(step A[c, n]) is exp(A[c, n] * that sum)); the carry kernel
 // turns the N entries into the incoming state; PASS 3 walks the chunk from it and writes the output.
-template <typename T, int NMAX, int PASS>
-__global__ void selective_chunk_kernel(const T* __restrict__ xc, const T* __restrict__ proj, int ld_proj, int z_col,
+// FULL: N == NMAX, which spares the kernel its question "n < N" at every state of every token.
+template <typename T, int NMAX, int PASS, bool FULL>
+__global__ void __launch_bounds__(64, NMAX <= 16 ? 16 : 1)  // small states: 64 registers, so that an SM holds 32 warps
+selective_chunk_kernel(const T* __restrict__ xc, const T* __restrict__ proj, int ld_proj, int z_col,
                                        const float* __restrict__ bc, const float* __restrict__ dt,
                                        const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                        const float* __restrict__ Dp, float* __restrict__ scratch,
@@ -354,36 +542,53 @@ __global__ void selective_chunk_kernel(const T* __restrict__ xc, const T* __rest
   float A[NMAX], S[NMAX];
 #pragma unroll
   for (int n = 0; n < NMAX; ++n) {
-    A[n] = n < N ? -expf(A_log[(size_t)c * N + n]) : 0.f;
-    S[n] = (PASS == 3 && n < N) ? sc[(size_t)n * I] : 0.f;
+    A[n] = (FULL || n < N) ? decay_rate<T>(A_log[(size_t)c * N + n]) : 0.f;
+    S[n] = (PASS == 3 && (FULL || n < N)) ? sc[(size_t)n * I] : 0.f;
   }
   const float db = dt_bias[c], dskip = PASS == 3 ? Dp[c] : 0.f;
   float sum_step = 0.f;
+  // a token's operands are asked for one token ahead, so that their way from memory is covered by the arithmetic of
+  // the token before (the blocks are small and few: nothing else would hide it)
+  float dt_n = dt[(size_t)t0 * I + c], x_n = to_float(xc[(size_t)t0 * I + c]);
+  float z_n = PASS == 3 ? to_float(proj[(size_t)t0 * ld_proj + z_col + c]) : 0.f;
+  float B_n[NMAX], C_n[NMAX];
+  load_row<NMAX>(bc + (size_t)t0 * 2 * N, N, B_n);
+  if (PASS == 3) load_row<NMAX>(bc + (size_t)t0 * 2 * N + N, N, C_n);
   for (int t = t0; t < t1; ++t) {
-    const float step = softplus_f(dt[(size_t)t * I + c] + db);
-    const float x = to_float(xc[(size_t)t * I + c]);
+    const float dt_c = dt_n, x = x_n, z = z_n;
+    float Bt[NMAX], Ct[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      Bt[n] = B_n[n];
+      if (PASS == 3) Ct[n] = C_n[n];
+    }
+    if (t + 1 < t1) {
+      dt_n = dt[(size_t)(t + 1) * I + c];
+      x_n = to_float(xc[(size_t)(t + 1) * I + c]);
+      if (PASS == 3) z_n = to_float(proj[(size_t)(t + 1) * ld_proj + z_col + c]);
+      load_row<NMAX>(bc + (size_t)(t + 1) * 2 * N, N, B_n);
+      if (PASS == 3) load_row<NMAX>(bc + (size_t)(t + 1) * 2 * N + N, N, C_n);
+    }
+    const float step = scan_softplus<T>(dt_c + db);
     const float sx = step * x;
-    const float* Bt = bc + (size_t)t * 2 * N;
-    const float* Ct = Bt + N;
     float y = 0.f;
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) {
-      if (n < N) {
-        S[n] = fmaf(expf(step * A[n]), S[n], sx * Bt[n]);
+      if (FULL || n < N) {
+        S[n] = fmaf(decay<T>(step, A[n]), S[n], sx * Bt[n]);
         if (PASS == 3) y = fmaf(S[n], Ct[n], y);
       }
     }
     if (PASS == 1) sum_step += step;
     if (PASS == 3) {
       y = fmaf(dskip, x, y);
-      const float z = to_float(proj[(size_t)t * ld_proj + z_col + c]);
-      out[(size_t)t * I + c] = from_float<T>(y * silu_f(z));
+      out[(size_t)t * I + c] = from_float<T>(y * scan_silu<T>(z));
     }
   }
   if (PASS == 1) {
 #pragma unroll
     for (int n = 0; n < NMAX; ++n)
-      if (n < N) sc[(size_t)n * I] = S[n];
+      if (FULL || n < N) sc[(size_t)n * I] = S[n];
     sc[(size_t)N * I] = sum_step;
   }
 }
@@ -406,10 +611,20 @@ __global__ void selective_carry_kernel(float* __restrict__ scratch, const float*
   float* sc = scratch + ((size_t)(q_start[b] / SCAN_CHUNK + b) * (N + 1)) * I + c;
   float* st = state + ((size_t)slot * N + n) * I + c;
   float S = live ? *st : 0.f;
-  for (int j = 0; j < chunks; ++j, sc += (size_t)(N + 1) * I) {
-    const float V = sc[(size_t)n * I], P = expf(A * sc[(size_t)N * I]);
-    sc[(size_t)n * I] = S;
-    S = fmaf(P, S, V);
+  const size_t pitch = (size_t)(N + 1) * I;
+  for (int j0 = 0; j0 < chunks; j0 += 8) {  // eight records are asked for together, then walked
+    float P[8], V[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const bool in = j0 + k < chunks;
+      V[k] = in ? sc[(j0 + k) * pitch + (size_t)n * I] : 0.f;
+      P[k] = in ? sc[(j0 + k) * pitch + (size_t)N * I] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (j0 + k < chunks) sc[(j0 + k) * pitch + (size_t)n * I] = S;
+      S = fmaf(expf(A * P[k]), S, V[k]);
+    }
   }
   if (live) *st = S;
 }
@@ -423,14 +638,19 @@ static int selective_chunked_launch(const void* xc, const void* proj, int ld_pro
   const int chunks = (max_q_len + SCAN_CHUNK - 1) / SCAN_CHUNK;
   dim3 grid(B, chunks, (I + threads - 1) / threads), cgrid(B, (I + threads - 1) / threads, N);
   if (chunks > 65535 || grid.z > 65535 || N > 65535) return Q3_ERR_SIZE;
-#define Q3_SC(NM)                                                                                                    \
+#define Q3_SC_GO(NM, FULL)                                                                                           \
   do {                                                                                                               \
-    q3::launch(selective_chunk_kernel<T, NM, 1>, grid, dim3(threads), 0, stream, (const T*)xc, (const T*)proj, ld_proj, \
-               z_col, bc, dt, dt_bias, A_log, Dp, scratch, q_start, (T*)out, I, N);                                  \
+    q3::launch(selective_chunk_kernel<T, NM, 1, FULL>, grid, dim3(threads), 0, stream, (const T*)xc, (const T*)proj,  \
+               ld_proj, z_col, bc, dt, dt_bias, A_log, Dp, scratch, q_start, (T*)out, I, N);                          \
     q3::launch(selective_carry_kernel, cgrid, dim3(threads), 0, stream, scratch, A_log, state, q_start, slot_ids, I, N, \
                num_slots, status);                                                                                   \
-    q3::launch(selective_chunk_kernel<T, NM, 3>, grid, dim3(threads), 0, stream, (const T*)xc, (const T*)proj, ld_proj, \
-               z_col, bc, dt, dt_bias, A_log, Dp, scratch, q_start, (T*)out, I, N);                                  \
+    q3::launch(selective_chunk_kernel<T, NM, 3, FULL>, grid, dim3(threads), 0, stream, (const T*)xc, (const T*)proj,  \
+               ld_proj, z_col, bc, dt, dt_bias, A_log, Dp, scratch, q_start, (T*)out, I, N);                          \
+  } while (0)
+#define Q3_SC(NM)              \
+  do {                         \
+    if (N == NM) Q3_SC_GO(NM, true); \
+    else Q3_SC_GO(NM, false);  \
   } while (0)
   if (N <= 8) Q3_SC(8);
   else if (N <= 16) Q3_SC(16);
@@ -438,6 +658,7 @@ static int selective_chunked_launch(const void* xc, const void* proj, int ld_pro
   else if (N <= 64) Q3_SC(64);
   else if (N <= 128) Q3_SC(128);
   else return Q3_ERR_SIZE;
+#undef Q3_SC_GO
 #undef Q3_SC
   return launch_status();
 }
@@ -474,10 +695,17 @@ extern "C" int q3_token_shift(const float* x, const float* mu, float* state, con
                               const int* slot_ids, void* out, int dtype, int T, int W, int num_slots, int* status,
                               cudaStream_t stream) {
   if (T <= 0 || W <= 0) return 0;
-  int threads = ((W + 31) / 32) * 32;
+  const bool vec = W % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)mu % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+                   (uintptr_t)out % 16 == 0;
+  int threads = (((vec ? W / 4 : W) + 31) / 32) * 32;
   if (threads > 256) threads = 256;
-  Q3_BY_DTYPE(dtype, q3::launch(q3::token_shift_kernel<E>, dim3(T), dim3(threads), 0, stream, x, mu, state, q_start, tok_seq,
-                                slot_ids, (E*)out, W, num_slots, status))
+  if (vec) {
+    Q3_BY_DTYPE(dtype, q3::launch(q3::token_shift_vec4_kernel<E>, dim3(T), dim3(threads), 0, stream, x, mu, state, q_start,
+                                  tok_seq, slot_ids, (E*)out, W, num_slots, status))
+  } else {
+    Q3_BY_DTYPE(dtype, q3::launch(q3::token_shift_kernel<E>, dim3(T), dim3(threads), 0, stream, x, mu, state, q_start,
+                                  tok_seq, slot_ids, (E*)out, W, num_slots, status))
+  }
   return q3::launch_status();
 }
 
@@ -491,12 +719,26 @@ extern "C" int q3_causal_conv(const void* x, int ldx, const float* in_bias, cons
   const int threads = 128;
   dim3 grid(T, (C + threads - 1) / threads), sgrid(B, (C + threads - 1) / threads);
   if (grid.y > 65535) return Q3_ERR_SIZE;
+  // many tokens in bfloat16: eight channels and a run of tokens per thread; the state is then renewed for every request
+  if (dtype == Q3_BF16 && T > B && T >= 4 * q3::CONV_RUN && C % 8 == 0 && K <= q3::CONV_KMAX && ldx % 8 == 0 &&
+      (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0) {
+    using bf16 = __nv_bfloat16;
+    const int lanes = C / 8;
+    const int wide = lanes < 128 ? ((lanes + 31) / 32) * 32 : 128;
+    dim3 vgrid((T + q3::CONV_RUN - 1) / q3::CONV_RUN, (lanes + wide - 1) / wide);
+    q3::launch(q3::causal_conv_bf16x8_kernel, vgrid, dim3(wide), 0, stream, (const bf16*)x, ldx, in_bias, w, bias,
+               (const float*)state, q_start, tok_seq, slot_ids, (bf16*)out, T, C, K, act, num_slots, status);
+    if (K > 1)
+      q3::launch(q3::conv_state_kernel<bf16>, sgrid, dim3(threads), 0, stream, (const bf16*)x, ldx, in_bias, state, q_start,
+                 slot_ids, C, K, num_slots, 1);
+    return q3::launch_status();
+  }
   Q3_BY_DTYPE(dtype, {
     q3::launch(q3::causal_conv_kernel<E>, grid, dim3(threads), 0, stream, (const E*)x, ldx, in_bias, w, bias, state,
                q_start, tok_seq, slot_ids, (E*)out, C, K, act, num_slots, status);
     if (K > 1 && T > B)  // T == B: every portion is a single token
       q3::launch(q3::conv_state_kernel<E>, sgrid, dim3(threads), 0, stream, (const E*)x, ldx, in_bias, state, q_start,
-                 slot_ids, C, K, num_slots);
+                 slot_ids, C, K, num_slots, 0);
   })
   return q3::launch_status();
 }
