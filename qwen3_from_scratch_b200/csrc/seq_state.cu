@@ -145,9 +145,10 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int ldx, const float
 
 // bfloat16, C a multiple of 8, K up to CONV_KMAX: a thread takes eight channels (16-byte loads and stores) and a run
 // of CONV_RUN tokens, keeps the taps and the window of the last K - 1 inputs in registers and slides the window from
-// token to token; at a request's first token of the step the window is refilled from the state.  The state is
+// token to token; at a request's first token of the step the window is refilled from the state.  All of the run's
+// inputs are asked for before the first is used, so that a thread has CONV_RUN loads in flight.  The state is
 // only read here, also for a portion of one token (conv_state_kernel renews every request's afterwards).
-constexpr int CONV_KMAX = 4, CONV_RUN = 16;
+constexpr int CONV_KMAX = 4, CONV_RUN = 8;  // the kernel is compiled for each number of taps up to CONV_KMAX
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -158,30 +159,45 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   }
 }
 
+template <int K>
 __global__ void causal_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ in_bias,
                                           const float* __restrict__ w, const float* __restrict__ bias,
                                           const float* __restrict__ state, const int* __restrict__ q_start,
                                           const int* __restrict__ tok_seq, const int* __restrict__ slot_ids,
-                                          __nv_bfloat16* __restrict__ out, int Ttot, int C, int K, int act, int num_slots,
+                                          __nv_bfloat16* __restrict__ out, int Ttot, int C, int act, int num_slots,
                                           int* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (c >= C) return;
   const int t0 = blockIdx.x * CONV_RUN, t1 = min(Ttot, t0 + CONV_RUN);
-  float taps[CONV_KMAX][8], ib[8], cb[8], win[CONV_KMAX - 1][8];  // win[0] the oldest of the K - 1 inputs before the token
+  float taps[K][8], ib[8], cb[8], win[K > 1 ? K - 1 : 1][8];  // win[0] the oldest of the K - 1 inputs before the token
+  {
+    // the thread's 8 K taps lie side by side in w ([C, K]); they and the biases come in 16-byte loads (c is a
+    // multiple of 8 and the launcher has checked the pointers), not one by one: a thread has only CONV_RUN tokens
+    // to spread this preamble over
+    float flat[8 * K];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    ib[e] = in_bias ? in_bias[c + e] : 0.f;
-    cb[e] = bias ? bias[c + e] : 0.f;
+    for (int i = 0; i < 2 * K; ++i) {
+      const float4 f = reinterpret_cast<const float4*>(w + (size_t)c * K)[i];
+      flat[4 * i] = f.x; flat[4 * i + 1] = f.y; flat[4 * i + 2] = f.z; flat[4 * i + 3] = f.w;
+    }
 #pragma unroll
-    for (int j = 0; j < CONV_KMAX; ++j) taps[j][e] = j < K ? w[(size_t)(c + e) * K + j] : 0.f;
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int j = 0; j < K; ++j) taps[j][e] = flat[e * K + j];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float4 a = in_bias ? reinterpret_cast<const float4*>(in_bias + c)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 b = bias ? reinterpret_cast<const float4*>(bias + c)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      ib[4 * i] = a.x; ib[4 * i + 1] = a.y; ib[4 * i + 2] = a.z; ib[4 * i + 3] = a.w;
+      cb[4 * i] = b.x; cb[4 * i + 1] = b.y; cb[4 * i + 2] = b.z; cb[4 * i + 3] = b.w;
+    }
   }
   // entry i of the window before token t, place `at` in its portion: the input `K - 1 - i` tokens back
   auto fill = [&](int t, int at, int slot) {
 #pragma unroll
-    for (int i = 0; i < CONV_KMAX - 1; ++i) {
-      if (i >= K - 1) break;
+    for (int i = 0; i < K - 1; ++i) {
       const int back = K - 1 - i;
       if (at - back >= 0) {
         float f[8];
@@ -189,16 +205,28 @@ __global__ void causal_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, i
 #pragma unroll
         for (int e = 0; e < 8; ++e) win[i][e] = f[e] + ib[e];
       } else {
-        const float* st = state + ((size_t)slot * (K - 1) + (K - 1 + at - back)) * C + c;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) win[i][e] = slot >= 0 ? st[e] : 0.f;
+        const float4* st = reinterpret_cast<const float4*>(state + ((size_t)(slot < 0 ? 0 : slot) * (K - 1) + (K - 1 + at - back)) * C + c);
+        const float4 lo = slot >= 0 ? st[0] : make_float4(0.f, 0.f, 0.f, 0.f), hi = slot >= 0 ? st[1] : lo;
+        win[i][0] = lo.x; win[i][1] = lo.y; win[i][2] = lo.z; win[i][3] = lo.w;
+        win[i][4] = hi.x; win[i][5] = hi.y; win[i][6] = hi.z; win[i][7] = hi.w;
       }
     }
   };
-  for (int t = t0; t < t1; ++t) {
-    const int b = tok_seq[t];
+  uint4 raw[CONV_RUN];
+  int seq[CONV_RUN];
+#pragma unroll
+  for (int i = 0; i < CONV_RUN; ++i) {
+    const int t = t0 + i;
+    raw[i] = t < t1 ? *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + c) : make_uint4(0, 0, 0, 0);
+    seq[i] = t < t1 ? tok_seq[t] : 0;
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_RUN; ++i) {
+    const int t = t0 + i;
+    if (t >= t1) break;
+    const int b = seq[i];
     const int at = t - q_start[b];
-    if (t == t0 || at == 0) {
+    if (i == 0 || at == 0) {
       int slot = slot_ids[b];
       if (slot < 0 || slot >= num_slots) {
         if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
@@ -207,15 +235,22 @@ __global__ void causal_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, i
       fill(t, at, slot);
     }
     float v[8], acc[8];
-    unpack8(*reinterpret_cast<const uint4*>(x + (size_t)t * ldx + c), v);
+    unpack8(raw[i], v);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       v[e] += ib[e];
       acc[e] = cb[e];
 #pragma unroll
-      for (int i = 0; i < CONV_KMAX - 1; ++i)
-        if (i < K - 1) acc[e] = fmaf(taps[i][e], win[i][e], acc[e]);
-      acc[e] = activate(fmaf(taps[K - 1][e], v[e], acc[e]), act);
+      for (int j = 0; j < K - 1; ++j) acc[e] = fmaf(taps[j][e], win[j][e], acc[e]);
+      acc[e] = fmaf(taps[K - 1][e], v[e], acc[e]);
+    }
+    // the result is rounded to bfloat16: the SiLU takes the hardware's exponential and reciprocal
+    if (act == Q3_ACT_SILU) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = acc[e] * __fdividef(1.0f, 1.0f + __expf(-acc[e]));
+    } else if (act != Q3_ACT_NONE) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = activate(acc[e], act);
     }
     uint4 pk;
     pk.x = pack_pair(acc[0], acc[1]);
@@ -224,10 +259,9 @@ __global__ void causal_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, i
     pk.w = pack_pair(acc[6], acc[7]);
     *reinterpret_cast<uint4*>(out + (size_t)t * C + c) = pk;
 #pragma unroll
-    for (int i = 0; i < CONV_KMAX - 1; ++i) {
-      if (i >= K - 1) break;
+    for (int j = 0; j < K - 1; ++j) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) win[i][e] = (i + 1 < K - 1) ? win[i + 1 < CONV_KMAX - 1 ? i + 1 : i][e] : v[e];
+      for (int e = 0; e < 8; ++e) win[j][e] = (j + 1 < K - 1) ? win[j + 1 < K - 1 ? j + 1 : j][e] : v[e];
     }
   }
 }
@@ -721,13 +755,19 @@ extern "C" int q3_causal_conv(const void* x, int ldx, const float* in_bias, cons
   if (grid.y > 65535) return Q3_ERR_SIZE;
   // many tokens in bfloat16: eight channels and a run of tokens per thread; the state is then renewed for every request
   if (dtype == Q3_BF16 && T > B && T >= 4 * q3::CONV_RUN && C % 8 == 0 && K <= q3::CONV_KMAX && ldx % 8 == 0 &&
-      (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0) {
+      (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+      (!in_bias || (uintptr_t)in_bias % 16 == 0) && (!bias || (uintptr_t)bias % 16 == 0)) {
     using bf16 = __nv_bfloat16;
     const int lanes = C / 8;
     const int wide = lanes < 128 ? ((lanes + 31) / 32) * 32 : 128;
     dim3 vgrid((T + q3::CONV_RUN - 1) / q3::CONV_RUN, (lanes + wide - 1) / wide);
-    q3::launch(q3::causal_conv_bf16x8_kernel, vgrid, dim3(wide), 0, stream, (const bf16*)x, ldx, in_bias, w, bias,
-               (const float*)state, q_start, tok_seq, slot_ids, (bf16*)out, T, C, K, act, num_slots, status);
+#define Q3_CONV(KK)                                                                                                  \
+  case KK:                                                                                                           \
+    q3::launch(q3::causal_conv_bf16x8_kernel<KK>, vgrid, dim3(wide), 0, stream, (const bf16*)x, ldx, in_bias, w, bias,    \
+               (const float*)state, q_start, tok_seq, slot_ids, (bf16*)out, T, C, act, num_slots, status);           \
+    break;
+    switch (K) { Q3_CONV(1) Q3_CONV(2) Q3_CONV(3) Q3_CONV(4) }
+#undef Q3_CONV
     if (K > 1)
       q3::launch(q3::conv_state_kernel<bf16>, sgrid, dim3(threads), 0, stream, (const bf16*)x, ldx, in_bias, state, q_start,
                  slot_ids, C, K, num_slots, 1);
