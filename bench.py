@@ -462,7 +462,7 @@ def measure_model(key, args, peaks, sample_clocks):
                "frac": flops / prefill_s / (peaks["bf16_tflops"] * 1e12)}
     print(f"[bench] {spec['name']} prompt of {PREFILL_TOKENS}: {prefill_s * 1e3:.2f} ms, {prefill['value']:.0f} tok/s, "
           f"{prefill['frac']:.2f} of the bf16 peak", file=sys.stderr, flush=True)
-    # the prompt step at two further lengths (the contract's figure stays the 2,048-token one)
+    # the prompt step at two further lengths (the headline's prompt figure stays the 2,048-token one)
     more = {}
     for tokens in (512, 4096):
         t = prefill_bench(engine, tokens, max(3, min(args.steps, 10)), args.warmup, vocab)

@@ -26,7 +26,7 @@ PAGE = 16
 def binupel_config(s):
     att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"],
                                           "vdim": s["dim"], "scale": s["dim"] ** -0.5,
-                                          "q_temp": {"coef": 0.5, "every": 128}},
+                                          "q_temp": {"coef": 0.3, "every": 256}},
            "mlp": {"kind": "dense", "ff": s["ff"]}}
     rec = {"type": "rglru", "mixer": {"width": s["width"], "blocks": s["width"] // 256, "conv": 4},
            "mlp": {"kind": "dense", "ff": s["ff"]}}

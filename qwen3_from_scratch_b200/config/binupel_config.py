@@ -9,7 +9,8 @@ config.json names the model with ``"architecture": "Binupel"`` and carries::
 
 ``type`` is ``attention`` (mixer: heads, kv_heads, dim, vdim, scale, q_temp: {coef, every}), ``rglru`` (width,
 blocks, conv) or ``mamba1`` (inner, state, dt_rank, conv).  A layer with ``weights_of: j`` runs layer j's
-tensors on a cache and state of its own.  Every number comes from the file; nothing is assumed about the
+tensors on a cache and state of its own; its sizes are read from layer j's entry (from the entry that j's own
+``weights_of`` leads to, if j has one).  Every number comes from the file; nothing is assumed about the
 order or the count of the layers.
 """
 
@@ -83,15 +84,35 @@ class BinupelConfig(ModelConfig):
         entries = data.get("layers")
         if not isinstance(entries, (list, tuple)) or not entries:
             raise ConfigError("config.json: 'layers' must be a non-empty list")
-        layers = []
         for i, entry in enumerate(entries):
+            if not isinstance(entry, Mapping):
+                raise ConfigError(f"config.json: layers[{i}] must be an object")
+        # whose tensors each entry runs: its own, or those of the entry that `weights_of` leads to
+        owner_of = []
+        for i, entry in enumerate(entries):
+            j, seen = i, set()
+            while entries[j].get("weights_of") is not None:
+                nxt = entries[j]["weights_of"]
+                if isinstance(nxt, bool) or not isinstance(nxt, int) or not 0 <= nxt < len(entries) or nxt == j or j in seen:
+                    raise ConfigError(f"config.json: layers[{i}]: weights_of must lead to a layer with tensors of its own, "
+                                      f"got {entries[i]['weights_of']!r}")
+                seen.add(j)
+                j = nxt
+            owner_of.append(j)
+        layers = []
+        for i, shown in enumerate(entries):
             where = f"layers[{i}]"
-            if not isinstance(entry, Mapping) or not isinstance(entry.get("mixer"), Mapping):
+            entry = entries[owner_of[i]]  # a sharing entry equals its owner's in everything but `weights_of`
+            if shown.get("type", entry.get("type")) != entry.get("type"):
+                raise ConfigError(f"config.json: {where}: a layer that runs layer {owner_of[i]}'s weights must be of its type")
+            if not isinstance(entry.get("mixer"), Mapping):
                 raise ConfigError(f"config.json: {where} must be an object with 'type' and 'mixer'")
             kind = entry.get("type")
             if kind not in MIXER_KEYS:
                 raise ConfigError(f"config.json: {where}: mixer type {kind!r} is not built (built: {', '.join(MIXER_KEYS)})")
             m = entry["mixer"]
+            if kind == "attention" and "vdim" not in m:
+                m = dict(m, vdim=m.get("dim"))  # the values are the keys
             sizes = {key: _int(where, m, key) for key in MIXER_KEYS[kind]}
             if kind == "attention":
                 if sizes["heads"] % sizes["kv_heads"]:
@@ -117,16 +138,7 @@ class BinupelConfig(ModelConfig):
                 if not isinstance(mlp, Mapping) or mlp.get("kind") != "dense":
                     raise ConfigError(f"config.json: {where}: mlp must be null or of kind 'dense', got {mlp!r}")
                 ff = _int(f"{where}.mlp", mlp, "ff")
-            shared = entry.get("weights_of")
-            if shared is not None:
-                if isinstance(shared, bool) or not isinstance(shared, int) or not 0 <= shared < i:
-                    raise ConfigError(f"config.json: {where}: weights_of must name an earlier layer, got {shared!r}")
-                owner = layers[shared]
-                if owner.weights_of is not None:
-                    raise ConfigError(f"config.json: {where}: weights_of names layer {shared}, which has no tensors of its own")
-                if (owner.type, owner.sizes(), owner.ff) != (kind, sizes, ff):
-                    raise ConfigError(f"config.json: {where}: a layer that runs layer {shared}'s weights must equal it")
-            layers.append(BinupelLayer(kind, tuple(sorted(sizes.items())), ff, shared))
+            layers.append(BinupelLayer(kind, tuple(sorted(sizes.items())), ff, None if owner_of[i] == i else owner_of[i]))
         eos = data.get("eos_token_id")
         return cls(architecture=ARCHITECTURE, vocab=vocab, width=width, norm_eps=eps, postln_alpha=alpha,
                    layers=tuple(layers), eos_token_id=eos if isinstance(eos, int) else None)

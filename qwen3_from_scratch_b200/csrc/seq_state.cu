@@ -295,7 +295,7 @@ __global__ void conv_state_kernel(const T* __restrict__ x, int ldx, const float*
 // shuffle reduction, the same for every number of tokens.  For few tokens and for the float32 path; many
 // tokens in bfloat16 go to the library's batched product.
 constexpr int BD_WARPS = 8;
-constexpr int BD_MAX_PER_LANE = 32;  // bw up to 1024
+constexpr int BD_MAX_PER_LANE = 32;  // rows of up to 1024 values stay in registers
 
 template <typename T>
 __global__ void __launch_bounds__(BD_WARPS * 32)
@@ -308,6 +308,16 @@ block_diag_kernel(const T* __restrict__ u, const T* __restrict__ w, float* __res
   if (unit >= nb * rows) return;
   const int blk = unit / rows, r = unit % rows;
   const T* wr = w + ((size_t)blk * rows + r) * bw;
+  if (bw > 32 * BD_MAX_PER_LANE) {  // a block too wide for the registers: its row is read again for every token
+    for (int t = 0; t < Ttot; ++t) {
+      const T* ur = u + (size_t)t * C + (size_t)blk * bw;
+      float dot = 0.f;
+      for (int e = lane; e < bw; e += 32) dot = fmaf(to_float(wr[e]), to_float(ur[e]), dot);
+      dot = warp_sum(dot);
+      if (lane == 0) out[((size_t)blk * Ttot + t) * rows + r] = dot;
+    }
+    return;
+  }
   float wv[BD_MAX_PER_LANE];
 #pragma unroll
   for (int k = 0; k < BD_MAX_PER_LANE; ++k) {
@@ -787,7 +797,7 @@ extern "C" int q3_causal_conv(const void* x, int ldx, const float* in_bias, cons
 extern "C" int q3_block_diag(const void* u, const void* w, float* out, int dtype, int T, int nb, int bw, int rows,
                              cudaStream_t stream) {
   if (T <= 0 || nb <= 0 || rows <= 0) return 0;
-  if (bw <= 0 || bw > 32 * q3::BD_MAX_PER_LANE) return Q3_ERR_SIZE;
+  if (bw <= 0) return Q3_ERR_SIZE;
   const int units = nb * rows;
   dim3 grid((units + q3::BD_WARPS - 1) / q3::BD_WARPS);
   Q3_BY_DTYPE(dtype, q3::launch(q3::block_diag_kernel<E>, grid, dim3(q3::BD_WARPS * 32), 0, stream, (const E*)u, (const E*)w,

@@ -37,7 +37,7 @@ def _mixer(kind: str, m: dict, cfg: BinupelConfig) -> PartSpec:
 def binupel_spec(cfg: BinupelConfig) -> ModelSpec:
     norm = PartSpec("rms_norm", {"dim": cfg.width, "eps": cfg.norm_eps, "suffix": ""})
     layers, order, index_of = [], [], {}
-    for i, layer in enumerate(cfg.layers):
+    for i, layer in enumerate(cfg.layers):  # first the layers with tensors of their own, whichever entries run them
         if layer.weights_of is None:
             ff = None if layer.ff is None else PartSpec("gated_mlp", {
                 "hidden_size": cfg.width, "intermediate_size": layer.ff, "activation": "relu", "names": _MLP_NAMES})
@@ -47,6 +47,7 @@ def binupel_spec(cfg: BinupelConfig) -> ModelSpec:
                 "names": _BLOCK_NAMES})
             index_of[i] = len(layers)
             layers.append((f"l{i}", block))
+    for i, layer in enumerate(cfg.layers):
         order.append(LayerCall(layer=index_of[i if layer.weights_of is None else layer.weights_of], cache=i))
     return ModelSpec(
         embedding=("embed", PartSpec("token_embedding", {"vocab_size": cfg.vocab, "hidden_size": cfg.width,

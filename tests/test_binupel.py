@@ -37,8 +37,9 @@ def test_configuration_round_trip_and_registry_by_single_name():
     (lambda c: c["layers"][1]["mixer"].update(blocks=5), "multiple"),
     (lambda c: c["layers"][0].update(type="hyena"), "not built"),
     (lambda c: c["layers"][0].update(mlp={"kind": "moe", "ff": 8}), "dense"),
-    (lambda c: c["layers"][3].update(weights_of=5), "earlier"),
-    (lambda c: c["layers"][3].update(mixer=dict(c["layers"][3]["mixer"], conv=9)), "must equal"),
+    (lambda c: c["layers"][3].update(weights_of=9), "weights_of"),
+    (lambda c: c["layers"][3].update(weights_of=3), "weights_of"),
+    (lambda c: c["layers"][3].update(type="attention"), "of its type"),
     (lambda c: c.pop("postln_alpha"), "postln_alpha"),
     (lambda c: c["norm"].pop("eps"), "eps"),
     (lambda c: c["layers"][2]["mixer"].pop("dt_rank"), "dt_rank"),
@@ -50,6 +51,24 @@ def test_configuration_errors_name_the_key(change, message):
     change(config)
     with pytest.raises(ConfigError, match=message):
         config_from_dict(config)
+
+
+def test_weights_of_may_lead_on_and_point_ahead():
+    """An entry's tensors are those of the entry its `weights_of` leads to, through another sharing entry or to a
+    later one; its own sizes are not read; `vdim` may be left out (the values are the keys)."""
+    from qwen3_from_scratch_b200.registry import config_from_dict
+    config = copy.deepcopy(BINUPEL_P)
+    config["layers"][0] = {"type": "rglru", "weights_of": 3}          # ahead, and 3 leads on to 1
+    del config["layers"][4]["mixer"]                                    # a sharing entry needs no sizes
+    config["layers"][4]["weights_of"] = 5
+    config["layers"][5] = {"type": "attention", "mlp": {"kind": "dense", "ff": 72},
+                           "mixer": {"heads": 4, "kv_heads": 2, "dim": 48, "scale": 0.21}}
+    cfg = config_from_dict(config)
+    assert [l.weights_of for l in cfg.layers] == [1, None, None, 1, 5, None]
+    assert cfg.layers[0].sizes() == cfg.layers[1].sizes() and cfg.layers[4].sizes()["vdim"] == 48
+    model = model_of(config)
+    assert [(c.layer, c.cache) for c in model.spec.order] == [(0, 0), (0, 1), (1, 2), (0, 3), (2, 4), (2, 5)]
+    assert config_from_dict(cfg.to_dict()) == cfg
 
 
 def test_run_order_and_cache_needs():
