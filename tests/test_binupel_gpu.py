@@ -401,6 +401,20 @@ def test_unequal_requests_together_equal_each_alone_with_pages_and_slots_used_ag
     assert_close(got, want, dtype, f"{key} mixed", tol=tolerance(dtype, cfg, w, seqs))
 
 
+def test_long_prompt_on_the_serving_kernels(folders):
+    """bfloat16, heads of 64 and 128 with pages of 16: a prompt of 700 tokens whole (several tiles of the tcgen05
+    portion attention, the scans in chunks, the tcgen05 gate/up product) and cut into long and short portions with
+    single tokens between them."""
+    cfg, w = plain.read_model_folder(folders["r"])
+    ids = tokens(cfg["vocab"], 700, 77)
+    want = {"a": plain.forward_logits(cfg, w, ids)}
+    tol = tolerance("bfloat16", cfg, w, {"a": ids})
+    for name, cuts in (("whole", [700]), ("portions", [300, 1, 250, 1, 1, 130, 17])):
+        got = replay(folders["r"], "bfloat16", {"a": ids}, lambda r, cuts=cuts: [r.step([("a", n)]) for n in cuts],
+                     page_size=16, num_pages=64, max_seqs=2, max_step_tokens=1024)
+        assert_close(got, want, "bfloat16", f"r long {name}", tol=tol)
+
+
 def test_long_decoding_through_graphs(folders):
     """300 single tokens after a short prompt, replayed from CUDA graphs: the states are carried on the device
     from step to step; the last logits still agree with the plain implementation in float32."""
