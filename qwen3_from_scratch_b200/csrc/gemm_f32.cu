@@ -1,8 +1,8 @@
 // True float32 matrix product for the 32-bit path of the model:
 //   C[M, N] = A[M, K] * W[N, K]^T      (the layout of a Linear weight: y = x W^T)
 // Plain FFMA on CUDA cores: no tensor cores, no TF32, no split-K.  Every output
-// element is the sum over k = 0..K-1 in ascending order, accumulated in one
-// register, so a row's result does not depend on M or on the rest of the batch.
+// element is the sum over k = 0..K-1 in ascending order, tile of 16 by tile of 16,
+// so a row's result does not depend on M or on the rest of the batch.
 // This is the slow, checkable path; the serving path uses tensor cores.
 #include "common.cuh"
 
@@ -37,6 +37,13 @@ gemm_f32_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, flo
       Ws[c][r] = (wn < N && k < K) ? W[(size_t)wn * ldw + k] : 0.f;
     }
     __syncthreads();
+    // the 16 products of a tile are summed on their own and the tile's sum is added to the total: the rounding
+    // error of a long reduction then grows with the number of tiles, not of terms (the order still depends on k alone)
+    float part[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < GF_BK; ++kk) {
       float a[4], b[4];
@@ -47,8 +54,12 @@ gemm_f32_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, flo
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
     __syncthreads();
   }
 #pragma unroll

@@ -337,6 +337,14 @@ block_diag_kernel(const T* __restrict__ u, const T* __restrict__ w, float* __res
   }
 }
 
+// a S + b for a = exp(log_a) in the float32 run.  A decay near 1 carries a state over thousands of tokens, and
+// expf's error of an ulp of 1 at every step would add up along the way; there the update is S + (b - (1 - a) S)
+// with 1 - a = -expm1(log_a), whose error is relative to 1 - a.  A fast decay (a below one half) keeps the
+// plain form, in which nothing of the size of the old state is added and taken away again.
+__device__ __forceinline__ float slow_decay_update(float log_a, float S, float b) {
+  return log_a > -0.6931472f ? S + fmaf(expm1f(log_a), S, b) : fmaf(expf(log_a), S, b);
+}
+
 // ---------------------------------------------------------------- gated linear recurrence (RG-LRU)
 // grid (requests, channel chunks), one thread per channel, tokens one after the other.
 // proj: [T, ld_proj], the y branch's pre-activation at column y_col; u: [T, C]; gates: float32 [nb, T, 2 bw]
@@ -369,9 +377,13 @@ __global__ void rglru_scan_kernel(const T* __restrict__ proj, int ld_proj, int y
     const float r = sigmoid_f(g[j] + rb);
     const float i = sigmoid_f(g[bw + j] + ib);
     const float log_a = rate * r;
-    const float a = expf(log_a);
     const float m = sqrtf(-expm1f(2.f * log_a));  // sqrt(1 - a^2) without the cancellation near a = 1
-    S = fmaf(a, S, m * i * to_float(u[(size_t)t * C + c]));
+    const float b = m * i * to_float(u[(size_t)t * C + c]);
+    if (sizeof(T) == 4) {
+      S = slow_decay_update(log_a, S, b);
+    } else {
+      S = fmaf(expf(log_a), S, b);
+    }
     const float y = gelu_tanh_f(to_float(proj[(size_t)t * ld_proj + y_col + c]) + yb);
     out[(size_t)t * C + c] = from_float<T>(S * y);
   }
@@ -461,7 +473,10 @@ __global__ void selective_scan_kernel(const T* __restrict__ xc, const T* __restr
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) {
       if (n < N) {
-        S[n] = fmaf(decay<T>(step, A[n]), S[n], sx * Bt[n]);
+        if (sizeof(T) == 4)  // see slow_decay_update
+          S[n] = slow_decay_update(step * A[n], S[n], sx * Bt[n]);
+        else
+          S[n] = fmaf(decay<T>(step, A[n]), S[n], sx * Bt[n]);
         y = fmaf(S[n], Ct[n], y);
       }
     }
