@@ -497,15 +497,24 @@ __global__ void selective_scan_kernel(const T* __restrict__ xc, const T* __restr
 // P_j S_in(j) + V_j (a loop of portion / SCAN_CHUNK steps), and each chunk is walked again from its S_in.
 // Chunk j of request b is filed at scratch index q_start[b] / SCAN_CHUNK + b + j, which never collides: a
 // request of n tokens has at most n / SCAN_CHUNK + 1 chunks.  The sums differ from the single walk's by float32
-// rounding; the float32 run keeps the single walk, so that its bits do not depend on the cut.
+// rounding; the float32 run keeps the single walk, so that its bits do not depend on the cut.  The chunked kernels
+// are the bfloat16 run's alone and take the hardware's special functions (see rglru_coeffs, decay, scan_softplus).
 constexpr int SCAN_CHUNK = 64;
+
+// The bfloat16 run's forms of the RG-LRU's functions: the hardware's exponential, reciprocal and tanh (float32
+// arithmetic, relative error near 2^-21; 1 - a^2 as written, whose rounding only matters where the term vanishes).
+__device__ __forceinline__ float fast_sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float fast_gelu_tanh_f(float z) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return 0.5f * z * (1.0f + t);
+}
 
 __device__ __forceinline__ void rglru_coeffs(float g_r, float g_i, float rb, float ib, float rate, float u, float& a,
                                              float& b) {
-  const float r = sigmoid_f(g_r + rb), i = sigmoid_f(g_i + ib);
-  const float log_a = rate * r;
-  a = expf(log_a);
-  b = sqrtf(-expm1f(2.f * log_a)) * i * u;
+  const float r = fast_sigmoid_f(g_r + rb), i = fast_sigmoid_f(g_i + ib);
+  a = __expf(rate * r);
+  b = sqrtf(fmaxf(1.0f - a * a, 0.f)) * i * u;
 }
 
 // PASS 1: the chunk's product and zero-start state into scratch [chunk][2][C].  PASS 3: the walk from the chunk's
@@ -536,7 +545,7 @@ __global__ void rglru_chunk_kernel(const T* __restrict__ proj, int ld_proj, int 
     S = fmaf(a, S, bb);
     if (PASS == 1) P *= a;
     if (PASS == 3) {
-      const float y = gelu_tanh_f(to_float(proj[(size_t)t * ld_proj + y_col + c]) + yb);
+      const float y = fast_gelu_tanh_f(to_float(proj[(size_t)t * ld_proj + y_col + c]) + yb);
       out[(size_t)t * C + c] = from_float<T>(S * y);
     }
   }
