@@ -116,6 +116,12 @@ MIXERS = {
               lambda h, ref, st: plain.rglru(h, ref, "", 3, st)),
     "selective_scan": ({"hidden_size": 40, "inner": 56, "state": 12, "dt_rank": 6, "conv": 3},
                        lambda h, ref, st: plain.selective_scan(h, ref, "", 6, st)),
+    # the edges of the sizes: a single tap (no tail to keep), one block of gates, an odd channel count; a state
+    # beyond 32, a step rank of 3, five taps (beyond the convolution kernel that is compiled per number of taps)
+    "rglru, one tap": ({"hidden_size": 40, "width": 44, "blocks": 1, "conv": 1},
+                       lambda h, ref, st: plain.rglru(h, ref, "", 1, st)),
+    "selective_scan, wide state": ({"hidden_size": 40, "inner": 24, "state": 40, "dt_rank": 3, "conv": 5},
+                                   lambda h, ref, st: plain.selective_scan(h, ref, "", 3, st)),
 }
 
 
@@ -125,7 +131,7 @@ def test_mixer_alone_whole_in_portions_and_beside_another_request(kind, dtype):
     from qwen3_from_scratch_b200.parts.base import PartSpec
     from qwen3_from_scratch_b200.registry import create_part
     params, plain_fn = MIXERS[kind]
-    bench = MixerBench(create_part("mixer", PartSpec(kind, params), name="m"), dtype, seed=11)
+    bench = MixerBench(create_part("mixer", PartSpec(kind.split(",")[0], params), name="m"), dtype, seed=11)
     g = torch.Generator().manual_seed(12)
     x_of = {r: torch.randn(n, 40, generator=g).to(DT[dtype]) for r, n in (("a", 41), ("b", 19))}
     want = {r: plain_fn(x.double(), bench.ref, None)[0] for r, x in x_of.items()}
@@ -288,10 +294,11 @@ def test_one_far_key_decides_the_output(dtype):
 
 # ---------------------------------------------------------------------- the tensor-core kernel against the plain one
 @pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 4), (6, 1, 48, 16), (8, 2, 64, 16), (8, 1, 128, 16), (4, 4, 128, 8),
-                                           (6, 2, 64, 32), (16, 1, 256, 8)])
+                                           (6, 2, 64, 32), (16, 1, 256, 8), (20, 1, 32, 16)])
 def test_tensor_core_sigmoid_attention_equals_the_plain_kernel(hq, hkv, d, page):
     """A mixed batch: three single tokens at contexts that end just before, at and just after a tile's and a page's
-    edge, and two portions (one from position 0, one continuing); key ranges of the decode form from 1 to many."""
+    edge, and two portions (one from position 0, one continuing); key ranges of the decode form from 1 to many.
+    (A group of more than 16 heads has no decode form: its single tokens run as portions of one.)"""
     from qwen3_from_scratch_b200.kernels import ops
     g = torch.Generator().manual_seed(41)
     q_lens, kv_lens = [1, 1, 1, 37, 150], [64, 65, 449, 37, 333]
