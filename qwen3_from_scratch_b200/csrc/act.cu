@@ -83,3 +83,59 @@ extern "C" int q3_swiglu(const void* gate_up, void* out, int dtype, int T, int I
                          cudaStream_t stream) {
   return q3_gated_act(gate_up, out, dtype, T, I, interleave8, Q3_ACT_SILU, stream);
 }
+
+namespace q3 {
+
+// out = act(x), element by element, evaluated in float32 (the feed-forward without a gate).
+template <typename T>
+__global__ void act_kernel(const T* __restrict__ x, T* __restrict__ out, size_t total, int act) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) out[i] = from_float<T>(activate(to_float(x[i]), act));
+}
+
+// Eight values per thread with 16-byte accesses (bfloat16, a multiple of eight values, aligned).
+__global__ void act_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, size_t total8,
+                                  int act) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total8) return;
+  const uint4 v = reinterpret_cast<const uint4*>(x)[i];
+  const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float a = __uint_as_float(in[k] << 16), b = __uint_as_float(in[k] & 0xffff0000u);
+    __nv_bfloat162 o = __floats2bfloat162_rn(activate(a, act), activate(b, act));
+    ow[k] = *reinterpret_cast<uint32_t*>(&o);
+  }
+  reinterpret_cast<uint4*>(out)[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
+}  // namespace q3
+
+// out = act(x) over `total` values in `dtype`; out may be x.
+extern "C" int q3_act(const void* x, void* out, int dtype, long long total, int act, cudaStream_t stream) {
+  if (act < Q3_ACT_SILU || act > Q3_ACT_GELU_TANH) return Q3_ERR_SIZE;
+  if (total <= 0) return 0;
+  const int threads = 256;
+  if (dtype == Q3_BF16 && total % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0) {
+    const size_t total8 = (size_t)total / 8;
+    q3::launch(q3::act_bf16x8_kernel, dim3((unsigned)((total8 + threads - 1) / threads)), dim3(threads), 0, stream,
+               (const __nv_bfloat16*)x, (__nv_bfloat16*)out, total8, act);
+    return q3::launch_status();
+  }
+  const long long blocks = (total + threads - 1) / threads;
+  if (blocks > 0x7fffffffll) return Q3_ERR_SIZE;
+  if (dtype == Q3_F32)
+    q3::launch(q3::act_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const float*)x, (float*)out,
+               (size_t)total, act);
+  else if (dtype == Q3_BF16)
+    q3::launch(q3::act_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)x,
+               (__nv_bfloat16*)out, (size_t)total, act);
+  else
+    return Q3_ERR_DTYPE;
+  return q3::launch_status();
+}

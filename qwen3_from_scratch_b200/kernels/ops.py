@@ -114,6 +114,27 @@ _SIGNATURES = {
     "q3_attn_sigmoid": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                         _c_void_p, _c_void_p],
+    "q3_embed_scaled": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p,
+                        _c_void_p],
+    "q3_hc_norm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                   _c_int, _c_float, _c_void_p, _c_void_p],
+    "q3_hc_sum_norm_rows": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                            _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "q3_softcap": [_c_void_p, _c_ll, _c_float, _c_void_p],
+    "q3_act": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_int, _c_void_p],
+    "q3_latent_kv_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                          _c_float, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                          _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "q3_latent_q_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p,
+                         _c_int, _c_int, _c_void_p],
+    "q3_latent_attn_ref": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                           _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "q3_gate_heads": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_ssd_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                    _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                    _c_void_p],
+    "q3_gated_group_norm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                            _c_float, _c_void_p],
 }
 
 
@@ -1265,3 +1286,232 @@ def sigmoid_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
             attn_sigmoid_tc(q, k_pages, v_pages, out, head_bias, gate, *rest)
         else:
             attn_sigmoid_mma(q, k_pages, v_pages, out, head_bias, gate, *rest)
+
+
+# ------------------------------------------------------------------ several residual streams
+HC_MAX_STREAMS = 8
+
+
+def embed_scaled(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float, status: torch.Tensor) -> None:
+    """out[t, s] = float32(table[ids[t]]) * scale for every stream s; out: float32 [T, S, W]."""
+    _check("embed_scaled.table", table)
+    _check("embed_scaled.ids", ids, torch.int32)
+    _check("embed_scaled.out", out, torch.float32)
+    T, S, W = out.shape
+    if table.shape[1] != W or ids.numel() != T:
+        raise KernelError(f"embed_scaled: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}")
+    code = library().q3_embed_scaled(table.data_ptr(), dtype_tag(table.dtype), ids.data_ptr(), out.data_ptr(), T, W,
+                                     table.shape[0], S, float(scale), status.data_ptr(), _stream())
+    _done("embed_scaled", code, f"streams {S}")
+
+
+def _hc_pending(name: str, pending, T: int, S: int, W: int, dtype: torch.dtype):
+    if pending is None:
+        return None, None, None
+    delta, mix, write = pending
+    _check(f"{name}.delta", delta, dtype)
+    _check(f"{name}.mix", mix, torch.float32)
+    _check(f"{name}.write", write, torch.float32)
+    if tuple(delta.shape) != (T, W) or tuple(mix.shape) != (S, S) or write.numel() != S:
+        raise KernelError(f"{name}: delta {tuple(delta.shape)}, mix {tuple(mix.shape)}, write {tuple(write.shape)} for "
+                          f"{S} streams of {T} x {W}")
+    return delta.data_ptr(), mix.data_ptr(), write.data_ptr()
+
+
+def hc_norm(streams: torch.Tensor, pending, read: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            status: torch.Tensor) -> None:
+    """``streams``: float32 [T, S, W].  With ``pending`` = (delta [T, W], mix [S, S] indexed [from, to], write [S])
+    the streams are first renewed in place, stream t <- sum_s mix[s, t] stream s + write[t] delta.  Then
+    out [T, W] = rmsnorm(sum_s read[s] stream s) * weight."""
+    _check("hc_norm.streams", streams, torch.float32)
+    _check("hc_norm.read", read, torch.float32)
+    _check("hc_norm.weight", weight, torch.float32)
+    _check("hc_norm.out", out)
+    T, S, W = streams.shape
+    if tuple(out.shape) != (T, W) or read.numel() != S or weight.numel() != W:
+        raise KernelError(f"hc_norm: streams {tuple(streams.shape)}, out {tuple(out.shape)}, read {tuple(read.shape)}")
+    d, m, wr = _hc_pending("hc_norm", pending, T, S, W, out.dtype)
+    code = library().q3_hc_norm(streams.data_ptr(), d, m, wr, read.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                dtype_tag(out.dtype), T, S, W, float(eps), status.data_ptr(), _stream())
+    _done("hc_norm", code, f"streams {S}")
+
+
+def hc_sum_norm_rows(streams: torch.Tensor, pending, weight: torch.Tensor, rows: torch.Tensor, out: torch.Tensor,
+                     eps: float, status: torch.Tensor) -> None:
+    """out [R, W] = rmsnorm(sum of the streams of row rows[r]) * weight, with ``pending`` (see ``hc_norm``)
+    applied to those rows first; the streams are left as they are."""
+    _check("hc_sum_norm_rows.streams", streams, torch.float32)
+    _check("hc_sum_norm_rows.weight", weight, torch.float32)
+    _check("hc_sum_norm_rows.rows", rows, torch.int32)
+    _check("hc_sum_norm_rows.out", out)
+    T, S, W = streams.shape
+    R = rows.numel()
+    if tuple(out.shape) != (R, W) or weight.numel() != W:
+        raise KernelError(f"hc_sum_norm_rows: streams {tuple(streams.shape)}, out {tuple(out.shape)}")
+    d, m, wr = _hc_pending("hc_sum_norm_rows", pending, T, S, W, out.dtype)
+    code = library().q3_hc_sum_norm_rows(streams.data_ptr(), d, m, wr, weight.data_ptr(), rows.data_ptr(), out.data_ptr(),
+                                         dtype_tag(out.dtype), T, R, S, W, float(eps), status.data_ptr(), _stream())
+    _done("hc_sum_norm_rows", code, f"streams {S}")
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), in place (float32)."""
+    _check("softcap.logits", logits, torch.float32)
+    code = library().q3_softcap(logits.data_ptr(), logits.numel(), float(cap), _stream())
+    _done("softcap", code, f"cap {cap}")
+
+
+def act(x: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = activation(x), element by element (evaluated in float32); ``out`` may be ``x``."""
+    _check("act.x", x)
+    _check("act.out", out, x.dtype)
+    if out.shape != x.shape:
+        raise KernelError(f"act: x {tuple(x.shape)}, out {tuple(out.shape)}")
+    code = library().q3_act(x.data_ptr(), out.data_ptr(), dtype_tag(x.dtype), x.numel(), activation_code(activation, gate=True),
+                            _stream())
+    _done("act", code)
+
+
+# ------------------------------------------------------------------ attention through a latent
+def latent_kv_post(proj: torch.Tensor, q_rank: int, kv_col: int, rank: int, rot: int, dims: int, gate_col: int, heads: int,
+                   q_norm: torch.Tensor, kv_norm: torch.Tensor, eps: float, freq: torch.Tensor, magnitude: float,
+                   positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor, c_pages: torch.Tensor,
+                   r_pages: torch.Tensor, cq: torch.Tensor, gate: torch.Tensor, write_cache: bool,
+                   status: torch.Tensor) -> None:
+    """From one product ``proj`` [T, ld] (query latent at column 0, kv latent and shared key part from ``kv_col``,
+    gate pre-activations from ``gate_col``): cq = rmsnorm(query latent) * q_norm; the normed kv latent and the key part
+    rotated by position into the pages ``c_pages`` [pages, 1, page, rank] and ``r_pages`` [pages, 1, page, rot];
+    gate [T, heads] = sigmoid (float32).  The first ``dims`` values of the key part are rotated (pairs i, i + dims / 2,
+    angle position * freq[i], sine and cosine times ``magnitude``)."""
+    _check("latent_kv_post.proj", proj)
+    _check("latent_kv_post.cq", cq, proj.dtype)
+    _check("latent_kv_post.c_pages", c_pages, proj.dtype)
+    _check("latent_kv_post.r_pages", r_pages, proj.dtype)
+    _check("latent_kv_post.gate", gate, torch.float32)
+    for name, t in (("q_norm", q_norm), ("kv_norm", kv_norm), ("freq", freq)):
+        _check(f"latent_kv_post.{name}", t, torch.float32)
+    for name, t in (("positions", positions), ("tok_seq", tok_seq), ("table", table)):
+        _check(f"latent_kv_post.{name}", t, torch.int32)
+    T, ld = proj.shape
+    page_size = c_pages.shape[2]
+    if (tuple(cq.shape) != (T, q_rank) or tuple(gate.shape) != (T, heads) or c_pages.shape[1] != 1 or c_pages.shape[3] != rank
+            or tuple(r_pages.shape) != (c_pages.shape[0], 1, page_size, rot) or q_norm.numel() != q_rank
+            or kv_norm.numel() != rank or freq.numel() * 2 != dims or kv_col < q_rank or kv_col + rank + rot > ld
+            or gate_col < 0 or gate_col + heads > ld or positions.numel() != T or tok_seq.numel() != T):
+        raise KernelError(f"latent_kv_post: proj {tuple(proj.shape)}, cq {tuple(cq.shape)}, c {tuple(c_pages.shape)}, "
+                          f"r {tuple(r_pages.shape)}, gate {tuple(gate.shape)}")
+    code = library().q3_latent_kv_post(
+        proj.data_ptr(), ld, int(q_rank), int(kv_col), int(rank), int(rot), int(dims), int(gate_col), int(heads),
+        q_norm.data_ptr(), kv_norm.data_ptr(), float(eps), freq.data_ptr(), float(magnitude), positions.data_ptr(),
+        tok_seq.data_ptr(), table.data_ptr(), table.shape[1], page_size, c_pages.shape[0], cq.data_ptr(),
+        c_pages.data_ptr(), r_pages.data_ptr(), gate.data_ptr(), 1 if write_cache else 0, dtype_tag(proj.dtype), T,
+        status.data_ptr(), _stream())
+    _done("latent_kv_post", code, f"ranks {q_rank}/{rank}, rot {rot}")
+
+
+def latent_q_post(q: torch.Tensor, heads: int, dim: int, rot: int, dims: int, freq: torch.Tensor, magnitude: float,
+                  positions: torch.Tensor, q_plain: torch.Tensor, q_rot: torch.Tensor) -> None:
+    """q [T, heads * (dim + rot)] -> q_plain [T, heads * dim] (as it is) and q_rot [T, heads, rot] (rotated by position)."""
+    _check("latent_q_post.q", q)
+    _check("latent_q_post.q_plain", q_plain, q.dtype)
+    _check("latent_q_post.q_rot", q_rot, q.dtype)
+    _check("latent_q_post.freq", freq, torch.float32)
+    _check("latent_q_post.positions", positions, torch.int32)
+    T = q.shape[0]
+    if (q.shape[1] != heads * (dim + rot) or tuple(q_plain.shape) != (T, heads * dim) or tuple(q_rot.shape) != (T, heads, rot)
+            or freq.numel() * 2 != dims or positions.numel() != T):
+        raise KernelError(f"latent_q_post: q {tuple(q.shape)}, q_plain {tuple(q_plain.shape)}, q_rot {tuple(q_rot.shape)}")
+    code = library().q3_latent_q_post(q.data_ptr(), int(heads), int(dim), int(rot), int(dims), freq.data_ptr(),
+                                      float(magnitude), positions.data_ptr(), q_plain.data_ptr(), q_rot.data_ptr(),
+                                      dtype_tag(q.dtype), T, _stream())
+    _done("latent_q_post", code, f"heads {heads} of {dim}+{rot}")
+
+
+def latent_attn_ref(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor, r_pages: torch.Tensor,
+                    positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float,
+                    status: torch.Tensor) -> None:
+    """Causal softmax attention over latents: q_abs float32 [H, T, rank] (the plain query taken through the key
+    up-projection), q_rot [T, H, rot]; score = (q_abs . c + q_rot . r) * scale over the keys 0 .. position of the
+    token's request; out [T, H * rank] = sum_j p_j c_j.  A warp per (token, head), keys one by one."""
+    _check("latent_attn_ref.q_abs", q_abs, torch.float32)
+    _check("latent_attn_ref.q_rot", q_rot)
+    _check("latent_attn_ref.c_pages", c_pages, q_rot.dtype)
+    _check("latent_attn_ref.r_pages", r_pages, q_rot.dtype)
+    _check("latent_attn_ref.out", out, q_rot.dtype)
+    for name, t in (("positions", positions), ("tok_seq", tok_seq), ("table", table)):
+        _check(f"latent_attn_ref.{name}", t, torch.int32)
+    H, T, rank = q_abs.shape
+    rot = q_rot.shape[2]
+    if (tuple(q_rot.shape) != (T, H, rot) or tuple(out.shape) != (T, H * rank) or c_pages.shape[1] != 1
+            or c_pages.shape[3] != rank or r_pages.shape[3] != rot or r_pages.shape[:3] != c_pages.shape[:3]):
+        raise KernelError(f"latent_attn_ref: q_abs {tuple(q_abs.shape)}, q_rot {tuple(q_rot.shape)}, c "
+                          f"{tuple(c_pages.shape)}, r {tuple(r_pages.shape)}, out {tuple(out.shape)}")
+    code = library().q3_latent_attn_ref(q_abs.data_ptr(), q_rot.data_ptr(), c_pages.data_ptr(), r_pages.data_ptr(),
+                                        positions.data_ptr(), tok_seq.data_ptr(), table.data_ptr(), table.shape[1],
+                                        c_pages.shape[2], c_pages.shape[0], out.data_ptr(), dtype_tag(out.dtype), T, H,
+                                        rank, rot, float(scale), status.data_ptr(), _stream())
+    _done("latent_attn_ref", code, f"heads {H}, rank {rank}, rot {rot}")
+
+
+def gate_heads(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, h * dv + v] = o[h, t, v] * gate[t, h]; o float32 [H, T, dv], gate float32 [T, H]."""
+    _check("gate_heads.o", o, torch.float32)
+    _check("gate_heads.gate", gate, torch.float32)
+    _check("gate_heads.out", out)
+    H, T, dv = o.shape
+    if tuple(gate.shape) != (T, H) or tuple(out.shape) != (T, H * dv):
+        raise KernelError(f"gate_heads: o {tuple(o.shape)}, gate {tuple(gate.shape)}, out {tuple(out.shape)}")
+    code = library().q3_gate_heads(o.data_ptr(), gate.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T, H, dv, _stream())
+    _done("gate_heads", code)
+
+
+# ------------------------------------------------------------------ state-space recurrence with a decay per head
+def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             d_skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int,
+             y: torch.Tensor, heads: int, vdim: int, n_state: int, groups: int, status: torch.Tensor) -> None:
+    """Per head h (group g = h // (heads / groups)): step = softplus(dt + dt_bias[h]); S <- exp(-exp(a_log[h]) step) S
+    + step B_g x_h^T; y_h = S^T C_g + d_skip[h] x_h.  xbc [T, ld]: x (heads * vdim columns), then B and C (groups *
+    n_state each); dt: proj[:, dt_col + h]; state float32 [slots, heads, n_state, vdim]; y float32 [T, heads * vdim]."""
+    _check("ssd_scan.xbc", xbc)
+    _check("ssd_scan.proj", proj, xbc.dtype)
+    _check("ssd_scan.y", y, torch.float32)
+    _check("ssd_scan.state", state, torch.float32)
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
+        _check(f"ssd_scan.{name}", t, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"ssd_scan: {name} has {t.numel()} values for {heads} heads")
+    T, ld = xbc.shape
+    inner = heads * vdim
+    if (ld != inner + 2 * groups * n_state or tuple(y.shape) != (T, inner) or proj.shape[0] != T or dt_col < 0
+            or dt_col + heads > proj.shape[1] or tuple(state.shape[1:]) != (heads, n_state, vdim)
+            or q_start.numel() < num_seqs + 1):
+        raise KernelError(f"ssd_scan: xbc {tuple(xbc.shape)}, proj {tuple(proj.shape)}, y {tuple(y.shape)}, state "
+                          f"{tuple(state.shape)}")
+    code = library().q3_ssd_scan(xbc.data_ptr(), ld, proj.data_ptr(), proj.shape[1], int(dt_col), dt_bias.data_ptr(),
+                                 a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), q_start.data_ptr(),
+                                 slot_ids.data_ptr(), y.data_ptr(), dtype_tag(xbc.dtype), T, int(num_seqs), heads, vdim,
+                                 n_state, groups, state.shape[0], status.data_ptr(), _stream())
+    _done("ssd_scan", code, f"heads {heads} x {vdim}, state {n_state}, groups {groups}")
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, z_col: int, weight: torch.Tensor, out: torch.Tensor, parts: int,
+                     eps: float) -> None:
+    """out = unit_rms_per_part(y * silu(z)) * weight: the row of I values is cut into ``parts`` equal parts, each divided
+    by its own root mean square.  y float32 [T, I]; z = z[:, z_col : z_col + I]."""
+    _check("gated_group_norm.y", y, torch.float32)
+    _check("gated_group_norm.z", z)
+    _check("gated_group_norm.out", out, z.dtype)
+    _check("gated_group_norm.weight", weight, torch.float32)
+    T, I = y.shape
+    if tuple(out.shape) != (T, I) or z.shape[0] != T or z_col < 0 or z_col + I > z.shape[1] or weight.numel() != I:
+        raise KernelError(f"gated_group_norm: y {tuple(y.shape)}, z {tuple(z.shape)}, out {tuple(out.shape)}")
+    code = library().q3_gated_group_norm(y.data_ptr(), z.data_ptr(), z.shape[1], int(z_col), weight.data_ptr(),
+                                         out.data_ptr(), dtype_tag(out.dtype), T, I, int(parts), float(eps), _stream())
+    _done("gated_group_norm", code, f"{parts} parts of {I}")
+
+
+def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor, r_pages: torch.Tensor, ctx,
+                     table: torch.Tensor, out: torch.Tensor, scale: float, status: torch.Tensor) -> None:
+    """Attention over latents for one step's batch (``ctx``: its positions, rows and lengths): see ``latent_attn_ref``
+    for the arithmetic.  Chooses the kernel."""
+    latent_attn_ref(q_abs, q_rot, c_pages, r_pages, ctx.positions, ctx.tok_seq, table, out, scale, status)

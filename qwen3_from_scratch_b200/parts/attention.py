@@ -1,5 +1,6 @@
-"""Grouped-query attention over a paged cache, with optional per-head RMSNorm of q and k,
-an optional position encoding, and an optional sliding window.
+"""Attention mixers over a paged cache: grouped-query softmax attention (with optional per-head RMSNorm of q and
+k, an optional position encoding and an optional sliding window), sigmoid attention whose values are its keys, and
+softmax attention through a latent (one latent vector and one rotated key part per token, shared by the heads).
 
 Reference: models/self_attn.py:300-386 (packed [T, hidden] input, merged QKV, head norm then
 rotation, keys/values written to pages, causal attention over the cache, output projection),
@@ -18,7 +19,7 @@ import torch
 
 from ..kernels import ops
 from ..registry import create_part, register_part
-from .base import KVCacheSpec, Mixer, PartSpec, Runtime, StepContext, WeightSpec
+from .base import CachePlane, KVCacheSpec, Mixer, PagedCacheSpec, PartSpec, Runtime, StepContext, WeightSpec
 from .linear import Linear
 
 
@@ -226,3 +227,105 @@ class SigmoidAttention(Mixer):
                               ctx.num_seqs, ctx.num_decode, ctx.max_q_len, ctx.max_kv_len, self.scale, self.rt.status,
                               partial=self._partial)
         return self.o_proj(out.view(T, hq * d))
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """Causal softmax attention whose keys and values are made from one latent vector per token (the multi-head
+    latent attention of DeepSeek-V2).  With h the input:
+
+        c_q = rmsnorm(W_dq h) w_q;   q = W_uq c_q, per head [dim plain | rot_dim rotated]
+        W_dkv h = [kv_rank values | rot_dim values]:  c = rmsnorm(first part) w_kv;  r = the rest, rotated, one for all heads
+        score(head) = (q_plain . W_uk,head c + q_rot . r) * scale;   value(head) = W_uv,head c
+        out = W_o concat_heads(sigmoid(W_g h)_head * softmax(scores) values)
+
+    Per token the cache holds only c (plane ``c``) and r (plane ``r``), one "head" each.  Keys and values are never
+    formed: the plain query is taken through W_uk once (q' = W_uk,head^T q_plain, ``kv_rank`` values), the kernels
+    attend over the latents themselves, and the result goes through W_uv,head afterwards.  ``scale`` is used as given.
+    Norms, angles, scores, weights and the gate are float32 in every run.  ``position``: a part with
+    ``frequencies()`` (``rotary_stretched``); ``names``: the tensors' names after the part's own."""
+
+    graph_capturable = True
+    NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
+             "gate": "g", "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
+                 q_rank: int, scale: float, norm_eps: float, position: PartSpec, names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.dim, self.rot_dim, self.vdim = int(dim), int(rot_dim), int(vdim)
+        self.kv_rank, self.q_rank = int(kv_rank), int(q_rank)
+        self.scale, self.norm_eps = float(scale), float(norm_eps)
+        self.position = create_part("position", position, name=f"{name}.position")
+        n = dict(self.NAMES)
+        n.update(names or {})
+        self.tensors = {k: f"{name}.{v}" for k, v in n.items()}
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, w, H = self.tensors, self.hidden_size, self.num_heads
+        return [WeightSpec(t["dq"], (self.q_rank, w)),
+                WeightSpec(t["dq_norm"], (self.q_rank,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["uq"], (H * (self.dim + self.rot_dim), self.q_rank)),
+                WeightSpec(t["dkv"], (self.kv_rank + self.rot_dim, w)),
+                WeightSpec(t["dkv_norm"], (self.kv_rank,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["uk"], (H * self.dim, self.kv_rank)),
+                WeightSpec(t["uv"], (H * self.vdim, self.kv_rank)),
+                WeightSpec(t["gate"], (H, w)),
+                WeightSpec(t["out"], (w, H * self.vdim))] + self.position.weight_specs()
+
+    def cache_spec(self) -> PagedCacheSpec:
+        return PagedCacheSpec((CachePlane("c", 1, self.kv_rank), CachePlane("r", 1, self.rot_dim)))
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        t, H = self.tensors, self.num_heads
+        dq, dkv, g = weights.pop(t["dq"]), weights.pop(t["dkv"]), weights.pop(t["gate"])
+        dtype = torch.float32 if torch.float32 in (dq.dtype, dkv.dtype, g.dtype) else dq.dtype
+        # one product reads the input: query latent, kv latent with the shared key part, gates (padded to whole
+        # groups of eight rows so that the few-rows product takes it)
+        rows = self.q_rank + self.kv_rank + self.rot_dim + H
+        pad = torch.zeros((-rows) % 8, dq.shape[1], dtype=dtype, device=dq.device)
+        self.down = Linear(torch.cat([dq.to(dtype), dkv.to(dtype), g.to(dtype), pad], dim=0), rt, tag="lattn.down")
+        del dq, dkv, g
+        self.kv_col, self.gate_col = self.q_rank, self.q_rank + self.kv_rank + self.rot_dim
+        self.q_norm, self.kv_norm = weights[t["dq_norm"]], weights[t["dkv_norm"]]
+        self.up_q = Linear(weights.pop(t["uq"]), rt, tag="lattn.uq")
+        uk, uv = weights.pop(t["uk"]), weights.pop(t["uv"])
+        # per head: W_uk^T [kv_rank, dim] takes the plain query into the latent's space, W_uv [vdim, kv_rank] brings
+        # the attended latent out; both in the compute dtype (a float32 run: float32)
+        self.uk_t = uk.view(H, self.dim, self.kv_rank).transpose(1, 2).to(rt.dtype).contiguous()
+        self.uv = uv.view(H, self.vdim, self.kv_rank).to(rt.dtype).contiguous()
+        del uk, uv
+        self.o_proj = Linear(weights.pop(t["out"]), rt, tag="lattn.o_proj")
+        self.position.setup(rt, weights)
+        T = rt.max_tokens
+        self._cq = rt.shared("lattn.cq", T, self.q_rank)
+        self._gate = rt.shared("lattn.gate", T, H, dtype=torch.float32)
+        self._q_plain = rt.shared("lattn.q_plain", T, H * self.dim)
+        self._q_rot = rt.shared("lattn.q_rot", T, H, self.rot_dim)
+        self._q_abs = rt.shared("lattn.q_abs", H * T * self.kv_rank, dtype=torch.float32)
+        self._o_lat = rt.shared("lattn.o_lat", T, H * self.kv_rank)
+        self._o_heads = rt.shared("lattn.o_heads", H * T * self.vdim, dtype=torch.float32)
+        self._o = rt.shared("lattn.o", T, H * self.vdim)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        T, H, rank, rot = x.shape[0], self.num_heads, self.kv_rank, self.rot_dim
+        planes, table = ctx.pages(cache_id)
+        c_pages, r_pages = planes["c"], planes["r"]
+        freq, mag, dims = self.position.frequencies()
+        status = self.rt.status
+        cq, gate = self._cq[:T], self._gate[:T]
+        ops.latent_kv_post(self.down(x), self.q_rank, self.kv_col, rank, rot, dims, self.gate_col, H, self.q_norm,
+                           self.kv_norm, self.norm_eps, freq, mag, ctx.positions, ctx.tok_seq, table, c_pages, r_pages, cq,
+                           gate, write_cache, status)
+        q_plain, q_rot = self._q_plain[:T], self._q_rot[:T]
+        ops.latent_q_post(self.up_q(cq), H, self.dim, rot, dims, freq, mag, ctx.positions, q_plain, q_rot)
+        q_abs = self._q_abs[: H * T * rank].view(H, T, rank)
+        ops.block_diag(q_plain, self.uk_t, q_abs)
+        o_lat = self._o_lat[:T]
+        ops.latent_attention(q_abs, q_rot, c_pages, r_pages, ctx, table, o_lat, self.scale, status)
+        o_heads = self._o_heads[: H * T * self.vdim].view(H, T, self.vdim)
+        ops.block_diag(o_lat, self.uv, o_heads)
+        out = self._o[:T]
+        ops.gate_heads(o_heads, gate, out)
+        return self.o_proj(out)

@@ -53,7 +53,7 @@ class WeightSpec:
                   held in float32 on the device whatever it was stored as.
       ``index``   integer table: held as int32.
     init: how the random-weights writer fills it (``normal``: N(0, 0.02);
-      ``one_plus_normal``: 1 + N(0, 0.1); ``zeros``).
+      ``one_plus_normal``: 1 + N(0, 0.1); ``zeros``; ``identity_plus_normal``: a matrix, I + N(0, 0.1)).
     """
 
     name: str
@@ -238,6 +238,16 @@ class StreamNorm:
     @property
     def dtype(self):
         return torch.bfloat16
+
+
+@dataclass
+class PendingStreamWrite:
+    """A sub-layer's output that has not reached the residual streams of a model with several of them yet:
+    stream t <- sum_s mix[s, t] stream s + write[t] delta.  The next norm kernel applies it on its way."""
+
+    delta: torch.Tensor  # [T, W] in the compute dtype
+    mix: torch.Tensor    # float32 [S, S], indexed [from, to]
+    write: torch.Tensor  # float32 [S]
 
 
 # ---------------------------------------------------------------------- parts

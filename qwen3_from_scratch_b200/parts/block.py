@@ -1,5 +1,6 @@
 """The arrangements of norms, mixer and feed-forward around the residual stream: the norm before each
-sub-layer (``pre_norm``) and the norm after each sub-layer's sum (``post_norm``, at the end of the file).
+sub-layer (``pre_norm``), the norm after each sub-layer's sum (``post_norm``), and the norm before each sub-layer
+of a model that keeps several residual streams per token (``hyper_pre_norm``, at the end of the file).
 
 Pre-norm residual block: h = x + mixer(norm1(x)); y = h + feed_forward(norm2(h)).
 
@@ -18,7 +19,8 @@ import torch
 
 from ..registry import create_part, register_part
 from ..kernels import ops
-from .base import NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, Runtime, StateSpec, StepContext, WeightSpec
+from .base import (NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, PendingStreamWrite, Runtime, StateSpec, StepContext,
+                   WeightSpec)
 
 
 @register_part("block", "pre_norm")
@@ -164,3 +166,81 @@ class PostNormBlock(Block):
             f = self.feed_forward.forward(x)
             self.norm2.scale_add_norm(stream, f, self.alpha, want_copy=False)
         return None
+
+
+@register_part("block", "hyper_pre_norm")
+class HyperPreNormBlock(Block):
+    """Pre-norm sub-layers over S residual streams per token (hyper-connections).  Sub-layer q (1: the mixer, 2: the
+    feed-forward) has three small tensors, ``<name>.hc<q>.in`` [S], ``.out`` [S] and ``.mix`` [S, S]:
+
+        u = sum_s in[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   (all t from the old x)
+
+    The streams are one float32 tensor [T, S, W].  A sub-layer's write stays open (``PendingStreamWrite``) until the
+    next norm kernel, which closes it, reads for the next sub-layer and norms in one pass over the streams; the block
+    hands its last write on to the block after it (or to the model's last norm) in the same way.  ``feed_forward``
+    may be None: the block is then the mixer alone."""
+
+    def __init__(self, name: str, norm1: PartSpec, mixer: PartSpec, streams: int, width: int,
+                 norm2: Optional[PartSpec] = None, feed_forward: Optional[PartSpec] = None,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        n = {"norm1": "norm1", "mixer": "mixer", "norm2": "norm2", "feed_forward": "feed_forward", "hc1": "hc1", "hc2": "hc2"}
+        n.update(names or {})
+        self.streams, self.width = int(streams), int(width)
+        if not 1 <= self.streams <= ops.HC_MAX_STREAMS:
+            raise ValueError(f"block {name}: between 1 and {ops.HC_MAX_STREAMS} residual streams, got {self.streams}")
+        self.norm1 = create_part("norm", norm1, name=f"{name}.{n['norm1']}")
+        self.mixer = create_part("mixer", mixer, name=f"{name}.{n['mixer']}")
+        self.feed_forward = self.norm2 = None
+        if feed_forward is not None:
+            if norm2 is None:
+                raise ValueError(f"block {name}: a feed-forward needs the norm before it")
+            self.norm2 = create_part("norm", norm2, name=f"{name}.{n['norm2']}")
+            self.feed_forward = create_part("feed_forward", feed_forward, name=f"{name}.{n['feed_forward']}")
+        self.hc = [f"{name}.{n['hc1']}", f"{name}.{n['hc2']}"]
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    @property
+    def graph_capturable(self) -> bool:
+        return all(p.graph_capturable for p in self._parts())
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [s for p in self._parts() for s in p.weight_specs()]
+        S = self.streams
+        for prefix in self.hc[: 2 if self.feed_forward is not None else 1]:
+            specs += [WeightSpec(f"{prefix}.in", (S,), kind="vector", init="one_plus_normal"),
+                      WeightSpec(f"{prefix}.out", (S,), kind="vector", init="one_plus_normal"),
+                      WeightSpec(f"{prefix}.mix", (S, S), kind="vector", init="identity_plus_normal")]
+        return specs
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        for part in self._parts():
+            part.setup(rt, weights)
+        self.coef = [(weights[f"{p}.in"], weights[f"{p}.out"], weights[f"{p}.mix"].contiguous())
+                     for p in self.hc[: 2 if self.feed_forward is not None else 1]]
+        self._normed = rt.shared("normed", rt.max_tokens, self.width)
+
+    def _read_norm(self, streams: torch.Tensor, pending: Optional[PendingStreamWrite], q: int, norm) -> torch.Tensor:
+        out = self._normed[: streams.shape[0]]
+        ops.hc_norm(streams, None if pending is None else (pending.delta, pending.mix, pending.write), self.coef[q][0],
+                    norm.weight, out, norm.eps, self.rt.status)
+        return out
+
+    def forward(self, stream: torch.Tensor, pending, ctx: StepContext, cache_id: Optional[int],
+                write_cache: bool) -> Optional[PendingStreamWrite]:
+        if stream.dim() != 3 or stream.shape[1] != self.streams:
+            raise ValueError(f"block {self.name}: expects {self.streams} residual streams per token, got a stream of "
+                             f"shape {tuple(stream.shape)}")
+        if pending is not None and not isinstance(pending, PendingStreamWrite):
+            raise ValueError(f"block {self.name}: the block before it left a plain sum open, not a write into streams")
+        x = self._read_norm(stream, pending, 0, self.norm1)
+        y = self.mixer.forward(x, ctx, cache_id, write_cache)
+        pending = PendingStreamWrite(y, self.coef[0][2], self.coef[0][1])
+        if self.feed_forward is not None:
+            x = self._read_norm(stream, pending, 1, self.norm2)
+            y = self.feed_forward.forward(x)
+            pending = PendingStreamWrite(y, self.coef[1][2], self.coef[1][1])
+        return pending

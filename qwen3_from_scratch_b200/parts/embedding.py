@@ -21,11 +21,17 @@ from .linear import Linear
 class TokenEmbedding(Part):
     graph_capturable = True
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int, suffix: str = ".weight"):
-        """``suffix``: what follows the part's name in its tensor's name ("" for a tensor named like the part)."""
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, suffix: str = ".weight", scale: float = 1.0,
+                 copies: int = 1):
+        """``suffix``: what follows the part's name in its tensor's name ("" for a tensor named like the part).
+        ``scale`` multiplies the looked-up rows.  With ``copies`` > 1 the model keeps that many residual streams per
+        token: the result is [T, copies, hidden], every stream starting as the same row."""
         super().__init__(name)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.tensor = f"{name}{suffix}"
+        self.scale, self.copies = float(scale), int(copies)
+        if self.copies < 1 or self.copies > ops.HC_MAX_STREAMS:
+            raise ValueError(f"embedding {name}: between 1 and {ops.HC_MAX_STREAMS} residual streams, got {self.copies}")
 
     def weight_specs(self) -> List[WeightSpec]:
         return [WeightSpec(self.tensor, (self.vocab_size, self.hidden_size))]
@@ -33,11 +39,16 @@ class TokenEmbedding(Part):
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
         self.weight = weights[self.tensor]
-        self._stream = rt.shared("stream", rt.max_tokens, self.hidden_size, dtype=torch.float32)
+        self.plain = self.copies == 1 and self.scale == 1.0
+        shape = (rt.max_tokens, self.hidden_size) if self.plain else (rt.max_tokens, self.copies, self.hidden_size)
+        self._stream = rt.shared("stream", *shape, dtype=torch.float32)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         stream = self._stream[: token_ids.numel()]
-        ops.embed(self.weight, token_ids, stream, self.rt.status)
+        if self.plain:
+            ops.embed(self.weight, token_ids, stream, self.rt.status)
+        else:
+            ops.embed_scaled(self.weight, token_ids, stream, self.scale, self.rt.status)
         return stream
 
 
@@ -45,13 +56,15 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     graph_capturable = True
 
-    """logits = x W^T in float32.  ``tied_to``: name of the embedding tensor it shares, or None."""
+    """logits = x W^T in float32.  ``tied_to``: name of the embedding tensor it shares, or None.
+    ``softcap``: logits <- softcap * tanh(logits / softcap), or None for the logits as they are."""
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None,
-                 suffix: str = ".weight"):
+                 suffix: str = ".weight", softcap: Optional[float] = None):
         super().__init__(name)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.tied_to = tied_to
+        self.softcap = None if softcap is None else float(softcap)
         self.tensor = f"{name}{suffix}"
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -65,4 +78,7 @@ class LMHead(Part):
         self.proj = Linear(weight, rt, out_dtype=torch.float32, reuse_output=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.proj(x)
+        logits = self.proj(x)
+        if self.softcap is not None:
+            ops.softcap(logits, self.softcap)
+        return logits

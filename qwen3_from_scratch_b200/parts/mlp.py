@@ -94,3 +94,35 @@ class GatedMLP(FeedForward):
 class SwiGLU(GatedMLP):
     def __init__(self, name: str, hidden_size: int, intermediate_size: int):
         super().__init__(name, hidden_size, intermediate_size, activation="silu")
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(FeedForward):
+    """Feed-forward without a gate: y = W_down act(W_up x), no biases.  ``names``: what follows the part's name (and
+    a dot) in the names of its up and down tensors."""
+
+    graph_capturable = True
+
+    def __init__(self, name: str, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh",
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        ops.activation_code(activation, gate=True)
+        self.activation = activation
+        n = {"up": "up_proj.weight", "down": "down_proj.weight"}
+        n.update(names or {})
+        self.tensors = {k: f"{name}.{v}" for k, v in n.items()}
+
+    def weight_specs(self) -> List[WeightSpec]:
+        h, i = self.hidden_size, self.intermediate_size
+        return [WeightSpec(self.tensors["up"], (i, h)), WeightSpec(self.tensors["down"], (h, i))]
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.up = Linear(weights.pop(self.tensors["up"]), rt, tag="ffn.up")
+        self.down = Linear(weights.pop(self.tensors["down"]), rt, tag="ffn.down")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        h = self.up(x)
+        ops.act(h, h, self.activation)
+        return self.down(h)

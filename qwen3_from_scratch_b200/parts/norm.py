@@ -66,3 +66,30 @@ class RMSNorm(Norm):
         out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)
         ops.add_rmsnorm_rows(stream, delta, self.weight, rows, out, self.eps)
         return out
+
+
+@register_part("norm", "stream_sum_rms_norm")
+class StreamSumRMSNorm(Norm):
+    """The last norm of a model with several residual streams per token: y = rmsnorm(sum of the streams) * w, for
+    chosen rows of ``streams`` [T, S, W].  What the last sub-layer left open (``PendingStreamWrite``: its output and
+    the coefficients that bring it into the streams) is applied to those rows on the way; the streams are not changed."""
+
+    graph_capturable = True
+
+    def __init__(self, name: str, dim: int, eps: float, streams: int, suffix: str = ".weight"):
+        super().__init__(name)
+        self.dim, self.eps, self.streams = int(dim), float(eps), int(streams)
+        self.tensor = f"{name}{suffix}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.tensor, (self.dim,), kind="vector", init="one_plus_normal")]
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.weight = weights[self.tensor]
+
+    def norm_rows(self, stream: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)
+        pending = None if delta is None else (delta.delta, delta.mix, delta.write)
+        ops.hc_sum_norm_rows(stream, pending, self.weight, rows, out, self.eps, self.rt.status)
+        return out

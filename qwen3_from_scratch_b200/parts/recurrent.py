@@ -171,3 +171,80 @@ class SelectiveScan(Mixer, _NamedTensors):
                            ctx.q_start, ctx.slot_ids, ctx.num_seqs, y, status, max_q_len=ctx.max_q_len,
                            scratch=self._chunks)
         return self.out_proj(y)
+
+
+@register_part("mixer", "ssd")
+class SSD(Mixer, _NamedTensors):
+    """The mixer of Mamba-2 (Dao and Gu, "Transformers are SSMs: Generalized Models and Efficient Algorithms Through
+    Structured State Space Duality"): a state-space recurrence with one scalar decay per head.  With inner =
+    heads * vdim, N = state, G = groups:
+
+        W_in h = [z: inner | x: inner | B: G N | C: G N | dt: heads];   [x | B | C] <- silu(conv([x | B | C]))
+        step = softplus(dt + dt_bias);   S_h <- exp(-exp(A_log_h) step) S_h + step B_g x_h^T   (S_h: N x vdim)
+        y_h = S_h^T C_g + D_h x_h;   out = W_o (unit_rms_per_part(y * silu(z)) * norm)
+
+    (head h reads group h // (heads / G); the gated y is cut into ``norm_groups`` equal parts, each divided by its
+    own root mean square).  Per request it keeps ``state`` (float32 [heads, N, vdim]) and ``conv`` (the last taps - 1
+    inputs of the convolution, float32); a new request's slot is zero.  Step sizes, decays, the state and the norm
+    are float32 in every run."""
+
+    graph_capturable = True
+    NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "a_log": "A_log", "d": "D",
+             "norm": "norm", "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, vdim: int, state: int, groups: int, norm_groups: int,
+                 conv: int, norm_eps: float, names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.num_heads, self.vdim = int(hidden_size), int(num_heads), int(vdim)
+        self.state_size, self.groups, self.norm_groups, self.taps = int(state), int(groups), int(norm_groups), int(conv)
+        self.norm_eps = float(norm_eps)
+        self.inner = self.num_heads * self.vdim
+        if self.num_heads % self.groups or self.inner % self.norm_groups:
+            raise ValueError(f"{self.num_heads} heads / {self.groups} groups / {self.norm_groups} norm groups do not divide")
+        self.channels = self.inner + 2 * self.groups * self.state_size  # what the convolution runs over
+        self._name_tensors(name, self.NAMES, names)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, w, H = self.tensors, self.hidden_size, self.num_heads
+        return [WeightSpec(t["in"], (self.inner + self.channels + H, w)),
+                WeightSpec(t["conv"], (self.channels, self.taps), kind="vector", init="normal"),
+                WeightSpec(t["conv_bias"], (self.channels,), kind="vector", init="normal"),
+                WeightSpec(t["dt_bias"], (H,), kind="vector", init="normal"),
+                WeightSpec(t["a_log"], (H,), kind="vector", init="normal"),
+                WeightSpec(t["d"], (H,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["norm"], (self.inner,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["out"], (w, self.inner))]
+
+    def cache_spec(self):
+        return {"state": StateSpec((self.num_heads, self.state_size, self.vdim), "float32"),
+                "conv": StateSpec((self.taps - 1, self.channels), "float32")}
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        t = self.tensors
+        w_in = weights.pop(t["in"])
+        pad = torch.zeros((-w_in.shape[0]) % 8, w_in.shape[1], dtype=w_in.dtype, device=w_in.device)
+        self.in_proj = Linear(torch.cat([w_in, pad], dim=0), rt, tag="ssd.in")  # columns: z, x, B, C, dt
+        del w_in
+        self.conv_weight, self.conv_bias = weights[t["conv"]], weights[t["conv_bias"]]
+        self.dt_bias, self.a_log, self.d_skip = weights[t["dt_bias"]], weights[t["a_log"]], weights[t["d"]]
+        self.norm_weight = weights[t["norm"]]
+        self.out_proj = Linear(weights.pop(t["out"]), rt, tag="ssd.out")
+        self._xbc = rt.shared("ssd.xbc", rt.max_tokens, self.channels)
+        self._y = rt.shared("ssd.y", rt.max_tokens, self.inner, dtype=torch.float32)
+        self._gated = rt.shared("ssd.gated", rt.max_tokens, self.inner)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        T, inner = x.shape[0], self.inner
+        status = self.rt.status
+        proj = self.in_proj(x)
+        xbc = self._xbc[:T]
+        ops.causal_conv(proj, inner, None, self.conv_weight, self.conv_bias, ctx.state(cache_id, "conv"), ctx.q_start,
+                        ctx.tok_seq, ctx.slot_ids, ctx.num_seqs, xbc, "silu", status)
+        y = self._y[:T]
+        ops.ssd_scan(xbc, proj, inner + self.channels, self.dt_bias, self.a_log, self.d_skip, ctx.state(cache_id, "state"),
+                     ctx.q_start, ctx.slot_ids, ctx.num_seqs, y, self.num_heads, self.vdim, self.state_size, self.groups,
+                     status)
+        gated = self._gated[:T]
+        ops.gated_group_norm(y, proj, 0, self.norm_weight, gated, self.norm_groups, self.norm_eps)
+        return self.out_proj(gated)

@@ -106,4 +106,4 @@ def _load_builtin() -> None:
     if not _builtin_loaded:
         _builtin_loaded = True
         from .parts import attention, block, embedding, mlp, norm, recurrent, rope  # noqa: F401  register themselves
-        from .models import binupel, qwen3  # noqa: F401  register the architectures
+        from .models import bikadra, binupel, qwen3  # noqa: F401  register the architectures

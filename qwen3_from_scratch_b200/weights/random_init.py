@@ -1,7 +1,8 @@
 """Random weights: writes a model folder (config.json + model.safetensors) from a configuration
 and a seed, so that the real loader is what every test and benchmark goes through.
 
-Matrices and embeddings are N(0, 0.02), norm weights 1 + N(0, 0.1).  Every tensor has a
+Matrices and embeddings are N(0, 0.02), norm weights 1 + N(0, 0.1), matrices that mix residual streams the
+identity + N(0, 0.1).  Every tensor has a
 generator of its own, seeded from (seed, tensor name), so a tensor's values do not depend on
 which other tensors the model has or on the order they are written in.
 
@@ -44,6 +45,8 @@ def random_tensor(spec: WeightSpec, seed: int, dtype: torch.dtype) -> torch.Tens
         t = 1.0 + torch.randn(spec.shape, generator=g, dtype=torch.float32) * 0.1
     elif spec.init == "zeros":
         t = torch.zeros(spec.shape, dtype=torch.float32)
+    elif spec.init == "identity_plus_normal":
+        t = torch.eye(spec.shape[0], spec.shape[1]) + torch.randn(spec.shape, generator=g, dtype=torch.float32) * 0.1
     else:
         raise ValueError(f"tensor '{spec.name}': unknown init '{spec.init}'")
     return t.to(dtype)
@@ -94,6 +97,9 @@ def random_weights_on_device(specs: Sequence[WeightSpec], seed: int, device, com
             t.normal_(1.0, 0.1, generator=g)
         elif spec.init == "zeros":
             t.zero_()
+        elif spec.init == "identity_plus_normal":
+            t.normal_(0.0, 0.1, generator=g)
+            t += torch.eye(spec.shape[0], spec.shape[1], dtype=dtype, device=device)
         else:
             raise ValueError(f"tensor '{spec.name}': unknown init '{spec.init}'")
         out[spec.name] = t
