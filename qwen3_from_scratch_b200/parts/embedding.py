@@ -22,15 +22,16 @@ class TokenEmbedding(Part):
     graph_capturable = True
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int, suffix: str = ".weight", scale: float = 1.0,
-                 copies: int = 1):
+                 copies: Optional[int] = None):
         """``suffix``: what follows the part's name in its tensor's name ("" for a tensor named like the part).
-        ``scale`` multiplies the looked-up rows.  With ``copies`` > 1 the model keeps that many residual streams per
-        token: the result is [T, copies, hidden], every stream starting as the same row."""
+        ``scale`` multiplies the looked-up rows.  With ``copies`` (a number, 1 included) the model's blocks keep that
+        many residual streams per token: the result is [T, copies, hidden], every stream starting as the same row;
+        None: the single stream [T, hidden] of the other blocks."""
         super().__init__(name)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.tensor = f"{name}{suffix}"
-        self.scale, self.copies = float(scale), int(copies)
-        if self.copies < 1 or self.copies > ops.HC_MAX_STREAMS:
+        self.scale, self.copies = float(scale), None if copies is None else int(copies)
+        if self.copies is not None and not 1 <= self.copies <= ops.HC_MAX_STREAMS:
             raise ValueError(f"embedding {name}: between 1 and {ops.HC_MAX_STREAMS} residual streams, got {self.copies}")
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -39,14 +40,16 @@ class TokenEmbedding(Part):
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
         self.weight = weights[self.tensor]
-        self.plain = self.copies == 1 and self.scale == 1.0
-        shape = (rt.max_tokens, self.hidden_size) if self.plain else (rt.max_tokens, self.copies, self.hidden_size)
+        self.plain = self.copies is None and self.scale == 1.0
+        shape = (rt.max_tokens, self.hidden_size) if self.copies is None else (rt.max_tokens, self.copies, self.hidden_size)
         self._stream = rt.shared("stream", *shape, dtype=torch.float32)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         stream = self._stream[: token_ids.numel()]
         if self.plain:
             ops.embed(self.weight, token_ids, stream, self.rt.status)
+        elif self.copies is None:
+            ops.embed_scaled(self.weight, token_ids, stream.unsqueeze(1), self.scale, self.rt.status)
         else:
             ops.embed_scaled(self.weight, token_ids, stream, self.scale, self.rt.status)
         return stream

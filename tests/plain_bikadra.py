@@ -243,8 +243,8 @@ def forward(config: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], states
             per_layer.append(xs.sum(dim=0))
     x = rms_norm(xs.sum(dim=0), w["final.norm"], config["norm"]["eps"])
     logits = linear(x, w["embed"])
-    cap = config["logit_softcap"]
-    return cap * torch.tanh(logits / cap), states
+    cap = config.get("logit_softcap")
+    return (logits if cap is None else cap * torch.tanh(logits / cap)), states
 
 
 def forward_logits(config: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> torch.Tensor:
