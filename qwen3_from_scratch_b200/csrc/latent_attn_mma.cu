@@ -1,0 +1,330 @@
+// Attention over cached latents on the tensor cores (bfloat16, mma.sync m16n8k16), for prompt portions and for
+// single tokens.  See latent_attn.cu for the arithmetic: every head's key is the token's latent c (`rank` values)
+// followed by the shared rotated part r (`rot` values), its value is c again, so one tile of keys in shared memory
+// serves all heads and all tokens of a request's portion.
+//
+// Rows are (token, head) pairs of one request, sixteen to a row group; a row group is four warps.  Per tile of
+// LM_KT keys:
+//   scores   the reduction over the rank + rot key values is cut into four ranges, one per warp, whose slice of
+//            the queries stays in registers as A fragments for the whole kernel (a row group reads a key tile
+//            once, not once per warp); the four partial score tiles meet in shared memory and every warp sums them
+//            in the same order;
+//   softmax  float32, every warp for the whole 16 x LM_KT tile (so no exchange of maxima), weights packed to
+//            bfloat16 A fragments in registers;
+//   output   the rank output columns are cut into four ranges, one per warp: O[16, rank / 4] += P V.
+// Key tiles are fetched with cp.async straight out of the pages, double-buffered.  With several key ranges per
+// request (single tokens over a long context) each range leaves (maximum, sum, unnormalised output) and
+// latent_attn_merge adds the ranges up in a fixed order.
+#include "attn_mma.cuh"
+
+namespace q3 {
+
+constexpr int LM_KT = 32;  // keys per tile
+
+// KS: k-steps of 16 per warp in the scores (rank + rot padded to 64 * KS); NO: pairs of 8-column output tiles per
+// warp (rank = 64 * NO); RG: row groups per block.
+template <int KS, int NO, int RG>
+__global__ void __launch_bounds__(RG * 128)
+latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ q_rot,
+                       const __nv_bfloat16* __restrict__ c_pages, const __nv_bfloat16* __restrict__ r_pages,
+                       const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ table,
+                       int stride, int page_size, int num_pages, __nv_bfloat16* __restrict__ out,
+                       float* __restrict__ partial, int Ttot, int H, int rank, int rot, float scale_log2, int splits,
+                       int* status) {
+  constexpr int DKP = 64 * KS, PITCH = DKP + 8, BM = 16 * RG;
+  extern __shared__ __align__(16) unsigned char lm_smem[];
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);                       // [2][LM_KT][PITCH]
+  float* sp = reinterpret_cast<float*>(lm_smem + (size_t)2 * LM_KT * PITCH * sizeof(__nv_bfloat16));  // [RG][4][16][LM_KT]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x, split = blockIdx.z;
+  const int t0 = q_start[b], q_len = q_start[b + 1] - t0;
+  const int R0 = blockIdx.y * BM;
+  if (R0 >= q_len * H) return;
+  const int kv = kv_len[b];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rg = warp >> 2, w = warp & 3, gid = lane >> 2, tid4 = lane & 3;
+  const int rows_total = q_len * H;
+  // this block's keys: everything the last of its tokens may see, cut into `splits` ranges of whole tiles
+  const int last_row = min(R0 + BM, rows_total) - 1;
+  const int keys = kv - q_len + last_row / H + 1;
+  const int tiles_all = (keys + LM_KT - 1) / LM_KT;
+  const int per = (tiles_all + splits - 1) / splits;
+  const int tile_lo = split * per, tile_hi = min(tiles_all, tile_lo + per);
+
+  // the two rows of this thread's fragments
+  int row_t[2], row_h[2], row_pos[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int R = R0 + rg * 16 + gid + 8 * r;
+    row_ok[r] = R < rows_total;
+    const int tq = row_ok[r] ? R / H : 0;
+    row_t[r] = t0 + tq;
+    row_h[r] = row_ok[r] ? R - tq * H : 0;
+    row_pos[r] = row_ok[r] ? kv - q_len + tq : -1;
+  }
+  // this warp's slice of the queries: columns w * 16 KS .. of [q_abs | q_rot | zeros]
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i & 1, d = (w * KS + ks) * 16 + 2 * tid4 + (i >> 1) * 8;
+      float v0 = 0.f, v1 = 0.f;
+      if (row_ok[r]) {
+        if (d < rank) {
+          const float2 v = *reinterpret_cast<const float2*>(q_abs + ((size_t)row_h[r] * Ttot + row_t[r]) * rank + d);
+          v0 = v.x;
+          v1 = v.y;
+        } else if (d < rank + rot) {
+          const __nv_bfloat162 v =
+              *reinterpret_cast<const __nv_bfloat162*>(q_rot + ((size_t)row_t[r] * H + row_h[r]) * rot + (d - rank));
+          v0 = __low2float(v);
+          v1 = __high2float(v);
+        }
+      }
+      qa[ks][i] = pack_bf16(v0, v1);
+    }
+
+  const int* trow = table + (size_t)b * stride;
+  auto load_tile = [&](int tile, int stage) {
+    __nv_bfloat16* dst = k_s + (size_t)stage * LM_KT * PITCH;
+    constexpr int CHUNKS = DKP / 8;
+    for (int i = threadIdx.x; i < LM_KT * CHUNKS; i += RG * 128) {
+      const int j = i / CHUNKS, c = i - j * CHUNKS;
+      const int n = tile * LM_KT + j, d = c * 8;
+      const __nv_bfloat16* src = c_pages;
+      int bytes = 0;
+      if (n < keys && d < rank + rot) {
+        const int page = table_page(trow, n / page_size, stride, status);
+        if (page >= 0 && page < num_pages) {
+          const size_t slot = (size_t)page * page_size + n % page_size;
+          src = d < rank ? c_pages + slot * rank + d : r_pages + slot * rot + (d - rank);
+          bytes = 16;
+        } else {
+          atomicOr(status, Q3_STATUS_BAD_PAGE);
+        }
+      }
+      cp_async_16(dst + (size_t)j * PITCH + d, src, bytes);
+    }
+  };
+
+  float o[2 * NO][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NO; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  if (tile_lo < tile_hi) load_tile(tile_lo, 0);
+  cp_async_commit();
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int stage = (tile - tile_lo) & 1;
+    if (tile + 1 < tile_hi) load_tile(tile + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* kt_s = k_s + (size_t)stage * LM_KT * PITCH;
+
+    // partial scores over this warp's range of the reduction
+    float s[LM_KT / 8][4];
+#pragma unroll
+    for (int i = 0; i < LM_KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+      for (int np = 0; np < LM_KT / 16; ++np) {
+        uint32_t kb[4];
+        ldmatrix_x4(kb, kt_s + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * PITCH + (w * KS + ks) * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * np], qa[ks], kb[0], kb[1]);
+        mma_bf16(s[2 * np + 1], qa[ks], kb[2], kb[3]);
+      }
+    }
+    float* mine = sp + ((size_t)(rg * 4 + w) * 16) * LM_KT;
+#pragma unroll
+    for (int nt = 0; nt < LM_KT / 8; ++nt)
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+        *reinterpret_cast<float2*>(mine + (gid + 8 * r) * LM_KT + nt * 8 + 2 * tid4) = make_float2(s[nt][2 * r], s[nt][2 * r + 1]);
+    __syncthreads();
+    // the whole tile's scores, summed in the order of the warps
+    const float* all = sp + ((size_t)rg * 4 * 16) * LM_KT;
+    const int base_n = tile * LM_KT;
+#pragma unroll
+    for (int nt = 0; nt < LM_KT / 8; ++nt)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int ww = 0; ww < 4; ++ww) {
+          const float2 v = *reinterpret_cast<const float2*>(all + ((size_t)ww * 16 + gid + 8 * r) * LM_KT + nt * 8 + 2 * tid4);
+          acc.x += v.x;
+          acc.y += v.y;
+        }
+        const int n = base_n + nt * 8 + 2 * tid4;
+        s[nt][2 * r] = n <= row_pos[r] ? acc.x * scale_log2 : -INFINITY;
+        s[nt][2 * r + 1] = n + 1 <= row_pos[r] ? acc.y * scale_log2 : -INFINITY;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < LM_KT / 8; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * r], s[nt][2 * r + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m[r], mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m[r] - m_use);
+      m[r] = m_new;
+      l[r] *= alpha;
+#pragma unroll
+      for (int i = 0; i < 2 * NO; ++i) {
+        o[i][2 * r] *= alpha;
+        o[i][2 * r + 1] *= alpha;
+      }
+#pragma unroll
+      for (int nt = 0; nt < LM_KT / 8; ++nt) {
+        const float p0 = exp2f(s[nt][2 * r] - m_use), p1 = exp2f(s[nt][2 * r + 1] - m_use);
+        s[nt][2 * r] = p0;
+        s[nt][2 * r + 1] = p1;
+        l[r] += p0 + p1;
+      }
+    }
+    // O[:, this warp's columns] += P V, V = the tile's latents
+#pragma unroll
+    for (int kk = 0; kk < LM_KT / 16; ++kk) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int dt = 0; dt < NO; ++dt) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, kt_s + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + (w * NO + dt) * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
+        mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();  // the stage and the score tiles may be written again
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    if (!row_ok[r]) continue;
+    const size_t row = (size_t)row_t[r] * H + row_h[r];
+    if (splits == 1) {
+      const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+      __nv_bfloat16* dst = out + row * rank + w * NO * 16 + 2 * tid4;
+#pragma unroll
+      for (int i = 0; i < 2 * NO; ++i)
+        *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = __floats2bfloat162_rn(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    } else {
+      float* dst = partial + (row * splits + split) * (rank + 2);
+      if (w == 0 && tid4 == 0) {
+        dst[0] = m[r];
+        dst[1] = l[r];
+      }
+#pragma unroll
+      for (int i = 0; i < 2 * NO; ++i)
+        *reinterpret_cast<float2*>(dst + 2 + w * NO * 16 + i * 8 + 2 * tid4) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+    }
+  }
+}
+
+// One block per (token, head): the key ranges' partial results added up in the order of the ranges.
+__global__ void latent_attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int rank,
+                                         int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t row = blockIdx.x;
+  const float* p = partial + row * splits * (rank + 2);
+  float mx = -INFINITY;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, p[(size_t)s * (rank + 2)]);
+  float total = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = p[(size_t)s * (rank + 2)];
+    if (ms != -INFINITY) total += p[(size_t)s * (rank + 2) + 1] * exp2f(ms - mx);
+  }
+  const float inv = total > 0.f ? 1.0f / total : 0.f;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = p[(size_t)s * (rank + 2)];
+      if (ms != -INFINITY) acc += p[(size_t)s * (rank + 2) + 2 + d] * exp2f(ms - mx);
+    }
+    out[row * rank + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int KS, int NO, int RG>
+static int lm_launch(const float* q_abs, const void* q_rot, const void* c_pages, const void* r_pages, const int* q_start,
+                     const int* kv_len, const int* table, int stride, int page_size, int num_pages, void* out,
+                     float* partial, int T, int B, int max_q_len, int H, int rank, int rot, float scale, int splits,
+                     int* status, cudaStream_t stream) {
+  using bf16 = __nv_bfloat16;
+  constexpr int PITCH = 64 * KS + 8;
+  const size_t smem = (size_t)2 * LM_KT * PITCH * sizeof(bf16) + (size_t)RG * 4 * 16 * LM_KT * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(latent_attn_mma_kernel<KS, NO, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured = true;
+  }
+  const long long tiles = ((long long)max_q_len * H + 16 * RG - 1) / (16 * RG);
+  if (tiles > 65535 || splits > 65535) return Q3_ERR_SIZE;
+  launch(latent_attn_mma_kernel<KS, NO, RG>, dim3(B, (unsigned)tiles, splits), dim3(RG * 128), smem, stream, q_abs,
+         (const bf16*)q_rot, (const bf16*)c_pages, (const bf16*)r_pages, q_start, kv_len, table, stride, page_size,
+         num_pages, (bf16*)out, partial, T, H, rank, rot, scale * 1.4426950408889634f, splits, status);
+  if (splits > 1) {
+    g_launch_early = false;  // started after every range has left its result
+    launch(latent_attn_merge_kernel, dim3((unsigned)((size_t)T * H)), dim3(128), 0, stream, (const float*)partial,
+           (bf16*)out, rank, splits);
+    g_launch_early = true;
+  }
+  return launch_status();
+}
+
+}  // namespace q3
+
+// 1 if the tensor-core kernel takes these sizes (bfloat16 only): a latent of 64, 128, 256 or 512 values and a
+// rotated part in multiples of 8 that fits the padded reduction.
+extern "C" int q3_latent_attn_mma_takes(int rank, int rot) {
+  if (rot < 0 || rot % 8) return 0;
+  const int dk = rank + rot;
+  if (rank == 512) return dk <= 576;
+  if (rank == 256) return dk <= 320;
+  if (rank == 128) return dk <= 192;
+  if (rank == 64) return dk <= 128;
+  return 0;
+}
+
+// q_abs: float32 [H, T, rank]; q_rot: bf16 [T, H, rot]; pages bf16; out: bf16 [T, H * rank].  `splits` key ranges per
+// request (1: the result is written at once; more: `partial` holds T * H * splits * (rank + 2) floats).  Every
+// request of the step reads the keys up to each of its tokens' positions (kv_len - q_len + index).
+extern "C" int q3_latent_attn_mma(const float* q_abs, const void* q_rot, const void* c_pages, const void* r_pages,
+                                  const int* q_start, const int* kv_len, const int* table, int stride, int page_size,
+                                  int num_pages, void* out, float* partial, int T, int B, int max_q_len, int H, int rank,
+                                  int rot, float scale, int splits, int* status, cudaStream_t stream) {
+  if (T <= 0 || B <= 0) return 0;
+  if (!q3_latent_attn_mma_takes(rank, rot) || H <= 0 || max_q_len <= 0 || page_size <= 0 || stride <= 0 || splits < 1)
+    return Q3_ERR_SIZE;
+  if (splits > 1 && !partial) return Q3_ERR_SCRATCH;
+  if ((uintptr_t)q_abs % 8 || (uintptr_t)q_rot % 4 || (uintptr_t)c_pages % 16 || (uintptr_t)r_pages % 16 ||
+      (uintptr_t)out % 4)
+    return Q3_ERR_ALIGN;
+  const bool wide = (long long)max_q_len * H > 16;  // more than one row group's rows per request
+#define Q3_LM(KS, NO)                                                                                                  \
+  return wide ? q3::lm_launch<KS, NO, 2>(q_abs, q_rot, c_pages, r_pages, q_start, kv_len, table, stride, page_size,    \
+                                         num_pages, out, partial, T, B, max_q_len, H, rank, rot, scale, splits, status, \
+                                         stream)                                                                       \
+              : q3::lm_launch<KS, NO, 1>(q_abs, q_rot, c_pages, r_pages, q_start, kv_len, table, stride, page_size,    \
+                                         num_pages, out, partial, T, B, max_q_len, H, rank, rot, scale, splits, status, \
+                                         stream);
+  if (rank == 512) { Q3_LM(9, 8) }
+  if (rank == 256) { Q3_LM(5, 4) }
+  if (rank == 128) { Q3_LM(3, 2) }
+  Q3_LM(2, 1)
+#undef Q3_LM
+}

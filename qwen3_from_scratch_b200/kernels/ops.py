@@ -129,6 +129,9 @@ _SIGNATURES = {
                          _c_int, _c_int, _c_void_p],
     "q3_latent_attn_ref": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                            _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "q3_latent_attn_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                           _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                           _c_void_p, _c_void_p],
     "q3_gate_heads": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_ssd_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
@@ -164,6 +167,8 @@ def library() -> ctypes.CDLL:
                 lib.q3_sm_count.restype = _c_int
                 lib.q3_attn_decode_blocks_per_sm.argtypes = [_c_int]
                 lib.q3_attn_decode_blocks_per_sm.restype = _c_int
+                lib.q3_latent_attn_mma_takes.argtypes = [_c_int, _c_int]
+                lib.q3_latent_attn_mma_takes.restype = _c_int
                 lib.q3_scan_chunk.argtypes = []
                 lib.q3_scan_chunk.restype = _c_int
                 lib.q3_sample_scratch_bytes.argtypes = [_c_int]
@@ -1510,8 +1515,61 @@ def gated_group_norm(y: torch.Tensor, z: torch.Tensor, z_col: int, weight: torch
     _done("gated_group_norm", code, f"{parts} parts of {I}")
 
 
+LATENT_MAX_SPLITS = 16  # key ranges per request of the single-token form
+LATENT_SPLIT_TILES = 4   # a range is at least so many tiles of 32 keys
+
+
+def latent_attention_fast(dtype: torch.dtype, rank: int, rot: int) -> bool:
+    """Whether the tensor-core kernel takes this latent: bfloat16, a latent of 64, 128, 256 or 512 values."""
+    return dtype == torch.bfloat16 and bool(library()._lib.q3_latent_attn_mma_takes(int(rank), int(rot)))
+
+
+def latent_partial_numel(num_seqs: int, heads: int, rank: int) -> int:
+    """Floats of scratch that the single-token form needs for its key ranges."""
+    return num_seqs * heads * LATENT_MAX_SPLITS * (rank + 2)
+
+
+def latent_decode_splits(num_seqs: int, heads: int, max_kv_len: int) -> int:
+    """Key ranges per request when every row brings one token: enough blocks to fill the device twice, a range no
+    shorter than ``LATENT_SPLIT_TILES`` tiles."""
+    blocks = num_seqs * -(-heads // 16)
+    by_length = max(1, -(-max_kv_len // 32) // LATENT_SPLIT_TILES)
+    return max(1, min(LATENT_MAX_SPLITS, by_length, -(-2 * sm_count() // blocks)))
+
+
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor, r_pages: torch.Tensor, ctx,
-                     table: torch.Tensor, out: torch.Tensor, scale: float, status: torch.Tensor) -> None:
+                     table: torch.Tensor, out: torch.Tensor, scale: float, status: torch.Tensor,
+                     partial: Optional[torch.Tensor] = None, kernel: str = "auto") -> None:
     """Attention over latents for one step's batch (``ctx``: its positions, rows and lengths): see ``latent_attn_ref``
-    for the arithmetic.  Chooses the kernel."""
-    latent_attn_ref(q_abs, q_rot, c_pages, r_pages, ctx.positions, ctx.tok_seq, table, out, scale, status)
+    for the arithmetic.  bfloat16 with a latent that ``latent_attention_fast`` takes runs on the tensor cores (rows of
+    (token, head) pairs over shared key tiles; with ``partial`` and a step of single tokens the keys of a request are
+    cut into ranges that run side by side and are merged); everything else, and float32, on the plain kernel.
+    ``kernel``: "auto", "plain" or "mma"."""
+    H, T, rank = q_abs.shape
+    rot = q_rot.shape[2]
+    fast = kernel != "plain" and latent_attention_fast(q_rot.dtype, rank, rot)
+    if kernel == "mma" and not fast:
+        raise KernelSizeError(f"latent_attention: the tensor-core kernel does not take rank {rank}, rot {rot}, {q_rot.dtype}")
+    if not fast:
+        latent_attn_ref(q_abs, q_rot, c_pages, r_pages, ctx.positions, ctx.tok_seq, table, out, scale, status)
+        return
+    _check("latent_attention.q_abs", q_abs, torch.float32)
+    _check("latent_attention.q_rot", q_rot, torch.bfloat16)
+    _check("latent_attention.c_pages", c_pages, torch.bfloat16)
+    _check("latent_attention.r_pages", r_pages, torch.bfloat16)
+    _check("latent_attention.out", out, torch.bfloat16)
+    if (tuple(q_rot.shape) != (T, H, rot) or tuple(out.shape) != (T, H * rank) or c_pages.shape[1] != 1
+            or c_pages.shape[3] != rank or r_pages.shape[3] != rot or r_pages.shape[:3] != c_pages.shape[:3]):
+        raise KernelError(f"latent_attention: q_abs {tuple(q_abs.shape)}, q_rot {tuple(q_rot.shape)}, c "
+                          f"{tuple(c_pages.shape)}, r {tuple(r_pages.shape)}, out {tuple(out.shape)}")
+    splits = 1
+    if ctx.max_q_len == 1 and partial is not None:
+        splits = latent_decode_splits(ctx.num_seqs, H, ctx.max_kv_len)
+        if partial.numel() < T * H * splits * (rank + 2):
+            splits = 1
+    code = library().q3_latent_attn_mma(
+        q_abs.data_ptr(), q_rot.data_ptr(), c_pages.data_ptr(), r_pages.data_ptr(), ctx.q_start.data_ptr(),
+        ctx.kv_len.data_ptr(), table.data_ptr(), table.shape[1], c_pages.shape[2], c_pages.shape[0], out.data_ptr(),
+        _ptr(partial) if splits > 1 else None, T, ctx.num_seqs, ctx.max_q_len, H, rank, rot, float(scale), splits,
+        status.data_ptr(), _stream())
+    _done("latent_attention (mma)", code, f"heads {H}, rank {rank}, rot {rot}, splits {splits}")

@@ -307,6 +307,10 @@ class LatentAttention(Mixer):
         self._o_lat = rt.shared("lattn.o_lat", T, H * self.kv_rank)
         self._o_heads = rt.shared("lattn.o_heads", H * T * self.vdim, dtype=torch.float32)
         self._o = rt.shared("lattn.o", T, H * self.vdim)
+        self._partial = None
+        if ops.latent_attention_fast(rt.dtype, self.kv_rank, self.rot_dim):
+            self._partial = rt.shared("lattn.partial", ops.latent_partial_numel(rt.max_seqs, H, self.kv_rank),
+                                      dtype=torch.float32)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         T, H, rank, rot = x.shape[0], self.num_heads, self.kv_rank, self.rot_dim
@@ -323,7 +327,7 @@ class LatentAttention(Mixer):
         q_abs = self._q_abs[: H * T * rank].view(H, T, rank)
         ops.block_diag(q_plain, self.uk_t, q_abs)
         o_lat = self._o_lat[:T]
-        ops.latent_attention(q_abs, q_rot, c_pages, r_pages, ctx, table, o_lat, self.scale, status)
+        ops.latent_attention(q_abs, q_rot, c_pages, r_pages, ctx, table, o_lat, self.scale, status, partial=self._partial)
         o_heads = self._o_heads[: H * T * self.vdim].view(H, T, self.vdim)
         ops.block_diag(o_lat, self.uv, o_heads)
         out = self._o[:T]

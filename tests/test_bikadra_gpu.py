@@ -307,6 +307,58 @@ def test_block_over_three_streams(dtype):
     close(got.transpose(0, 1), want, dtype, "streams after the block")
 
 
+# ---------------------------------------------------------------------- the tensor-core kernel against the plain one
+@pytest.mark.parametrize("H,rank,rot,page", [(16, 128, 64, 16), (5, 64, 32, 4), (17, 64, 64, 8), (16, 512, 64, 16),
+                                             (40, 256, 32, 16), (1, 128, 8, 32)])
+def test_tensor_core_latent_attention_equals_the_plain_kernel(H, rank, rot, page):
+    """bfloat16: a batch of a long portion, a portion that ends exactly on a tile's edge, a short one and two single
+    tokens, scattered over pages in another order than the tokens'; then single tokens alone with their keys cut
+    into ranges that are merged."""
+    from types import SimpleNamespace
+    from qwen3_from_scratch_b200.kernels import ops
+    assert ops.latent_attention_fast(torch.bfloat16, rank, rot)
+    g = torch.Generator().manual_seed(H * 1000 + rank)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
+
+    def batch(q_lens, kv_lens):
+        B, T = len(q_lens), sum(q_lens)
+        need = [-(-n // page) for n in kv_lens]
+        pages = sum(need) + 3
+        order = torch.randperm(pages, generator=g).tolist()
+        table = torch.full((B, max(need) + 1), -1, dtype=torch.int32)
+        at = 0
+        for b, n in enumerate(need):
+            table[b, :n] = torch.tensor(order[at:at + n], dtype=torch.int32)
+            at += n
+        c_pages = torch.randn(pages, 1, page, rank, generator=g).to(torch.bfloat16).cuda()
+        r_pages = torch.randn(pages, 1, page, rot, generator=g).to(torch.bfloat16).cuda()
+        q_abs = (torch.randn(H, T, rank, generator=g) * 0.5).cuda()
+        q_rot = (torch.randn(T, H, rot, generator=g) * 0.5).to(torch.bfloat16).cuda()
+        starts = [0] + torch.tensor(q_lens).cumsum(0).tolist()
+        ctx = SimpleNamespace(
+            positions=i32([kv_lens[b] - q_lens[b] + i for b in range(B) for i in range(q_lens[b])]),
+            tok_seq=i32([b for b in range(B) for _ in range(q_lens[b])]), q_start=i32(starts), kv_len=i32(kv_lens),
+            num_seqs=B, max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+        return q_abs, q_rot, c_pages, r_pages, ctx, table.cuda(), T
+
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scale = (rank + rot) ** -0.5
+    for q_lens, kv_lens, scratch in (([70, 32, 3, 1, 1], [200, 64, 3, 77, 1], False), ([1, 1, 1], [300, 1, 33], True),
+                                     ([1], [1500], True)):
+        q_abs, q_rot, c_pages, r_pages, ctx, table, T = batch(q_lens, kv_lens)
+        want = torch.empty(T, H * rank, dtype=torch.bfloat16, device="cuda")
+        ops.latent_attention(q_abs, q_rot, c_pages, r_pages, ctx, table, want, scale, status, kernel="plain")
+        got = torch.full_like(want, float("nan"))
+        partial = torch.empty(ops.latent_partial_numel(len(q_lens), H, rank), device="cuda") if scratch else None
+        if scratch and max(kv_lens) > 1000:
+            assert ops.latent_decode_splits(len(q_lens), H, max(kv_lens)) > 1
+        ops.latent_attention(q_abs, q_rot, c_pages, r_pages, ctx, table, got, scale, status, partial=partial, kernel="mma")
+        assert int(status.item()) == 0
+        # the tensor-core kernel rounds the absorbed query and each weight to bfloat16; both round the output once
+        scale_of = float(want.float().abs().max())
+        assert float((got.float() - want.float()).abs().max()) <= 1.5e-2 * scale_of, (q_lens, kv_lens)
+
+
 # ---------------------------------------------------------------------- whole models
 def tolerance(dtype, cfg, w, seqs):
     """float32: the harness's bound.  bfloat16: three times what rounding alone does to these prompts in the plain
