@@ -1,10 +1,11 @@
-"""``bench.py --arch binupel``: the Binupel design beside Qwen3 at equal layer sizes (random weights drawn on
+"""``bench.py --arch binupel|bikadra``: another design beside Qwen3 at equal layer sizes (random weights drawn on
 the device): a prompt step of 2,048 tokens and decode steps at two batch sizes, each replayed on the device
 between CUDA events, and every kernel of one eagerly launched step timed by events of its own, with the bytes
 or flops it must move and the fraction of the measured copy bandwidth or bf16 throughput that this makes.
 
-A Binupel model of ``layers`` entries repeats the pattern selective scan, RG-LRU, attention; the Qwen3 model
-has as many layers of the same width, heads, head size and feed-forward width.
+A Binupel model of ``layers`` entries repeats the pattern selective scan, RG-LRU, attention; a Bikadra model
+alternates the state-space mixer and attention through a latent, over four residual streams; the Qwen3 model has as
+many layers of the same width, heads, head size and feed-forward width.
 """
 
 from __future__ import annotations
@@ -35,6 +36,24 @@ def binupel_config(s):
     pattern = [scan, rec, att]
     return {"architecture": "Binupel", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
             "postln_alpha": 2.0, "layers": [pattern[i % 3] for i in range(s["layers"])]}
+
+
+def bikadra_config(s):
+    """State-space mixer and latent attention in turn: heads of 64 channels over twice the width with a state of 128
+    in eight groups; a latent of 512 with a rotated part of 64 and heads of 128 + 64 query and 128 value dimensions."""
+    ssm = {"type": "mamba2", "mixer": {"heads": 2 * s["width"] // 64, "vdim": 64, "state": 128, "groups": 8,
+                                       "norm_groups": 8, "conv": 4},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    att = {"type": "latent_attention",
+           "mixer": {"heads": s["heads"], "dim": s["dim"], "rot_dim": 64, "vdim": s["dim"], "kv_rank": 512,
+                     "q_rank": 3 * s["width"] // 4, "scale": (s["dim"] + 64) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": 64,
+                             "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    pattern = [ssm, att]
+    return {"architecture": "Bikadra", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0},
+            "streams": 4, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": [pattern[i % 2] for i in range(s["layers"])]}
 
 
 def qwen3_config(s):
@@ -138,6 +157,34 @@ class KernelClock:
             return "flops", 2 * x.shape[0] * w.shape[0] * w.shape[1]
         if name == "embed":
             return "bytes", size(a[2]) * 1.5
+        if name == "embed_scaled":
+            return "bytes", size(a[2]) * (1 + 0.5 / a[2].shape[1])
+        if name == "hc_norm":
+            streams, pending, out = a[0], a[1], a[4]
+            return "bytes", size(streams) * (2 if pending is not None else 1) + size(out) * (2 if pending is not None else 1)
+        if name == "act":
+            return "bytes", size(a[0]) + size(a[1])
+        if name == "latent_kv_post":
+            proj, c_pages, r_pages, cq, gate = a[0], a[16], a[17], a[18], a[19]
+            return "bytes", size(proj) + size(cq) + size(gate) + proj.shape[0] * (c_pages.shape[3] + r_pages.shape[3]) * 2
+        if name == "latent_q_post":
+            return "bytes", 2 * size(a[0])
+        if name == "gate_heads":
+            return "bytes", size(a[0]) + size(a[1]) + size(a[2])
+        if name == "latent_attention":
+            q_abs, q_rot, c_pages = a[0], a[1], a[2]
+            H, _, rank = q_abs.shape
+            rot = q_rot.shape[2]
+            if sc["kind"] == "prefill":
+                return "flops", 2 * H * (2 * rank + rot) * sc["tokens"] * (sc["tokens"] + 1) // 2
+            return "bytes", sc["batch"] * sc["context"] * (rank + rot) * c_pages.element_size() + size(q_abs) + size(a[6])
+        if name == "ssd_scan":
+            xbc, y = a[0], a[10]
+            twice = 2 if k.get("scratch") is not None and sc["kind"] == "prefill" else 1
+            return "bytes", twice * size(xbc) + size(y)
+        if name == "gated_group_norm":
+            y, out = a[0], a[4]
+            return "bytes", size(y) + 2 * size(out)
         return "bytes", 0
 
     def wrap(self, owner, attr, name):
@@ -161,7 +208,8 @@ class KernelClock:
         for name in ("embed", "add_rmsnorm", "add_rmsnorm_rows", "scale_add_rmsnorm", "token_shift", "causal_conv",
                      "gated_act", "swiglu", "qk_gate_post", "qkv_post", "gemm_tc_qkv", "rglru_scan", "selective_scan",
                      "sigmoid_attention", "paged_attention", "block_diag", "gemm_skinny", "gemm_skinny_normed",
-                     "gemm_skinny_into_stream", "gemm_tc"):
+                     "gemm_skinny_into_stream", "gemm_tc", "embed_scaled", "hc_norm", "act", "latent_kv_post",
+                     "latent_q_post", "gate_heads", "latent_attention", "ssd_scan", "gated_group_norm"):
             self.wrap(ops, name, name)
         real_mm = torch.mm
         clock = self
@@ -248,12 +296,13 @@ def compare(args, peaks, sample_clocks):
                  "decode_b64_ctx2048": {"kind": "decode", "batch": 64, "context": 2048}}
     sampler = sample_clocks()
     t0 = time.time()
-    out = {"arch": "binupel", "beside": "qwen3", "sizes": dict(size, name=args.arch_size), "dtype": "bf16",
+    other = {"binupel": binupel_config, "bikadra": bikadra_config}[args.arch]
+    out = {"arch": args.arch, "beside": "qwen3", "sizes": dict(size, name=args.arch_size), "dtype": "bf16",
            "data": "synthetic tokens, random weights drawn on the device", "steps": args.steps, "warmup": args.warmup,
            "peaks": peaks, "timing": "CUDA events around each replay of the step; 256 MB written between replays",
-           "binupel": {}, "qwen3": {}}
+           args.arch: {}, "qwen3": {}}
     for name, scenario in scenarios.items():
-        for model, config in (("binupel", binupel_config(size)), ("qwen3", qwen3_config(size))):
+        for model, config in ((args.arch, other(size)), ("qwen3", qwen3_config(size))):
             out[model][name] = run_scenario(config, scenario, args.steps, args.warmup, peaks)
             print(f"[bench] {model} {name}: {out[model][name]['ms_per_step']} ms", file=sys.stderr, flush=True)
     out["clocks"] = sampler.stop()

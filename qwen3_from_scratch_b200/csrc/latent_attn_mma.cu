@@ -20,6 +20,7 @@
 namespace q3 {
 
 constexpr int LM_KT = 32;  // keys per tile
+constexpr int LM_SP = LM_KT + 8;  // row pitch of the partial score tiles: eight rows of a warp's store fall on distinct banks
 
 // KS: k-steps of 16 per warp in the scores (rank + rot padded to 64 * KS); NO: pairs of 8-column output tiles per
 // warp (rank = 64 * NO); RG: row groups per block.
@@ -34,7 +35,7 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
   constexpr int DKP = 64 * KS, PITCH = DKP + 8, BM = 16 * RG;
   extern __shared__ __align__(16) unsigned char lm_smem[];
   __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);                       // [2][LM_KT][PITCH]
-  float* sp = reinterpret_cast<float*>(lm_smem + (size_t)2 * LM_KT * PITCH * sizeof(__nv_bfloat16));  // [RG][4][16][LM_KT]
+  float* sp = reinterpret_cast<float*>(lm_smem + (size_t)2 * LM_KT * PITCH * sizeof(__nv_bfloat16));  // [RG][4][16][LM_SP]
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, split = blockIdx.z;
@@ -88,25 +89,31 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
     }
 
   const int* trow = table + (size_t)b * stride;
+  // LM_KT keys by RG * 128 threads: a key's row is copied by TPK threads, which look its page up once
+  constexpr int TPK = RG * 128 / LM_KT, CHUNKS = DKP / 8;
+  const int load_j = threadIdx.x / TPK, load_c = threadIdx.x % TPK;
   auto load_tile = [&](int tile, int stage) {
-    __nv_bfloat16* dst = k_s + (size_t)stage * LM_KT * PITCH;
-    constexpr int CHUNKS = DKP / 8;
-    for (int i = threadIdx.x; i < LM_KT * CHUNKS; i += RG * 128) {
-      const int j = i / CHUNKS, c = i - j * CHUNKS;
-      const int n = tile * LM_KT + j, d = c * 8;
-      const __nv_bfloat16* src = c_pages;
-      int bytes = 0;
-      if (n < keys && d < rank + rot) {
-        const int page = table_page(trow, n / page_size, stride, status);
-        if (page >= 0 && page < num_pages) {
-          const size_t slot = (size_t)page * page_size + n % page_size;
-          src = d < rank ? c_pages + slot * rank + d : r_pages + slot * rot + (d - rank);
-          bytes = 16;
-        } else {
-          atomicOr(status, Q3_STATUS_BAD_PAGE);
-        }
+    __nv_bfloat16* dst = k_s + ((size_t)stage * LM_KT + load_j) * PITCH;
+    const int n = tile * LM_KT + load_j;
+    const __nv_bfloat16* c_src = c_pages;
+    const __nv_bfloat16* r_src = r_pages;
+    bool ok = false;
+    if (n < keys) {
+      const int page = table_page(trow, n / page_size, stride, status);
+      if (page >= 0 && page < num_pages) {
+        const size_t slot = (size_t)page * page_size + n % page_size;
+        c_src = c_pages + slot * rank;
+        r_src = r_pages + slot * rot;
+        ok = true;
+      } else if (load_c == 0) {
+        atomicOr(status, Q3_STATUS_BAD_PAGE);
       }
-      cp_async_16(dst + (size_t)j * PITCH + d, src, bytes);
+    }
+#pragma unroll
+    for (int c = load_c; c < CHUNKS; c += TPK) {
+      const int d = c * 8;
+      const bool real = ok && d < rank + rot;
+      cp_async_16(dst + d, real ? (d < rank ? c_src + d : r_src + (d - rank)) : c_pages, real ? 16 : 0);
     }
   };
 
@@ -139,15 +146,15 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
         mma_bf16(s[2 * np + 1], qa[ks], kb[2], kb[3]);
       }
     }
-    float* mine = sp + ((size_t)(rg * 4 + w) * 16) * LM_KT;
+    float* mine = sp + ((size_t)(rg * 4 + w) * 16) * LM_SP;
 #pragma unroll
     for (int nt = 0; nt < LM_KT / 8; ++nt)
 #pragma unroll
       for (int r = 0; r < 2; ++r)
-        *reinterpret_cast<float2*>(mine + (gid + 8 * r) * LM_KT + nt * 8 + 2 * tid4) = make_float2(s[nt][2 * r], s[nt][2 * r + 1]);
+        *reinterpret_cast<float2*>(mine + (gid + 8 * r) * LM_SP + nt * 8 + 2 * tid4) = make_float2(s[nt][2 * r], s[nt][2 * r + 1]);
     __syncthreads();
     // the whole tile's scores, summed in the order of the warps
-    const float* all = sp + ((size_t)rg * 4 * 16) * LM_KT;
+    const float* all = sp + ((size_t)rg * 4 * 16) * LM_SP;
     const int base_n = tile * LM_KT;
 #pragma unroll
     for (int nt = 0; nt < LM_KT / 8; ++nt)
@@ -156,7 +163,7 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
         float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
         for (int ww = 0; ww < 4; ++ww) {
-          const float2 v = *reinterpret_cast<const float2*>(all + ((size_t)ww * 16 + gid + 8 * r) * LM_KT + nt * 8 + 2 * tid4);
+          const float2 v = *reinterpret_cast<const float2*>(all + ((size_t)ww * 16 + gid + 8 * r) * LM_SP + nt * 8 + 2 * tid4);
           acc.x += v.x;
           acc.y += v.y;
         }
@@ -266,7 +273,7 @@ static int lm_launch(const float* q_abs, const void* q_rot, const void* c_pages,
                      int* status, cudaStream_t stream) {
   using bf16 = __nv_bfloat16;
   constexpr int PITCH = 64 * KS + 8;
-  const size_t smem = (size_t)2 * LM_KT * PITCH * sizeof(bf16) + (size_t)RG * 4 * 16 * LM_KT * sizeof(float);
+  const size_t smem = (size_t)2 * LM_KT * PITCH * sizeof(bf16) + (size_t)RG * 4 * 16 * LM_SP * sizeof(float);
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(latent_attn_mma_kernel<KS, NO, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

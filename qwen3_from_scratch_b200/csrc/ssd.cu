@@ -7,9 +7,11 @@
 // x, B and C come from one buffer `xbc` [T, ld] (x: heads * P columns at 0, then groups * N of B, then of C), dt
 // from column dt_col of `proj`.  Step sizes, decays and the state are float32 in every run.
 //
-// ssd_scan: a group of L lanes (a power of two, 16 states each) per (head, channel) walks a request's portion
-// token by token; the lanes' parts of y meet in a butterfly of shuffles whose order is the same for every cut of
-// a prompt, so the float32 run's bits do not depend on the cut.
+// ssd_scan: a group of L lanes (a power of two, 16 states each) per head and run of channels walks a request's
+// portion token by token; the lanes' parts of y meet in a butterfly of shuffles whose order is the same for every
+// cut of a prompt, so the float32 run's bits do not depend on the cut.  The bfloat16 run cuts long portions into
+// chunks that run side by side (the recurrence is linear in the state: a chunk is summarised by the product of its
+// decays and the state it reaches from zero), and takes the hardware's exponential and logarithm.
 // gated_group_norm: y * silu(z), divided by the root mean square of its part (the row is cut into equal parts),
 // times a weight.
 #include "common.cuh"
@@ -17,6 +19,7 @@
 namespace q3 {
 
 constexpr int SSD_PER = 16;  // states per lane
+constexpr int SSD_CHUNK = 64;  // tokens per chunk of the chunked form
 
 // a S + b with a = exp(log_a): see the note on slowly decaying states in seq_state.cu (the float32 run takes the
 // form whose error is relative to 1 - a).
@@ -25,61 +28,137 @@ __device__ __forceinline__ float ssd_update(float log_a, float a, float S, float
   return fmaf(a, S, b);
 }
 
-template <typename T>
+// SSD_PER values of row[col ..] as floats; VEC: bfloat16 with col a multiple of 8 and an aligned row (two 16-byte loads).
+template <typename T, bool VEC>
+__device__ __forceinline__ void ssd_load16(const T* __restrict__ row, int col, int live, float (&v)[SSD_PER]) {
+  if constexpr (VEC) {
+    if (live <= 0) {  // a lane beyond the last state (the lanes are a power of two): nothing of its own to read
+#pragma unroll
+      for (int i = 0; i < SSD_PER; ++i) v[i] = 0.f;
+      return;
+    }
+    const uint4 lo = *reinterpret_cast<const uint4*>(row + col), hi = *reinterpret_cast<const uint4*>(row + col + 8);
+    const uint32_t wds[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = __uint_as_float(wds[i] << 16);
+      v[2 * i + 1] = __uint_as_float(wds[i] & 0xffff0000u);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < SSD_PER; ++i) v[i] = i < live ? to_float(row[col + i]) : 0.f;
+  }
+}
+
+// A group of L lanes (a power of two, 16 states each) per (head, PP channels).  MODE 0: a request's whole portion from
+// its slot's state, which is renewed.  MODE 1 (blockIdx.z = chunk): the chunk from a zero state; leaves the state it
+// reaches and the product of its decays in `scratch`.  MODE 2: the chunk from the state that the carry left in
+// `scratch`; writes y.  A record of `scratch` is H * N * P + H floats; chunk j of request b is record
+// q_start[b] / SSD_CHUNK + b + j.
+template <typename T, int PP, bool VEC, int MODE>
 __global__ void __launch_bounds__(128)
 ssd_scan_kernel(const T* __restrict__ xbc, int ld, const T* __restrict__ proj, int ld_proj, int dt_col,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dp,
-                float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ slot_ids,
-                float* __restrict__ y, int H, int P, int N, int G, int L, int num_slots, int* status) {
+                float* __restrict__ state, float* __restrict__ scratch, const int* __restrict__ q_start,
+                const int* __restrict__ slot_ids, float* __restrict__ y, int H, int P, int N, int G, int L, int num_slots,
+                int* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x;
+  int t0 = q_start[b], t1 = q_start[b + 1];
+  size_t record = 0;
+  if (MODE != 0) {
+    record = (size_t)(t0 / SSD_CHUNK + b + blockIdx.z) * ((size_t)H * N * P + H);
+    t0 += blockIdx.z * SSD_CHUNK;
+    if (t0 >= t1) return;
+    t1 = min(t1, t0 + SSD_CHUNK);
+  }
+  const int PC = P / PP;
   const long long idx = (long long)blockIdx.y * blockDim.x + threadIdx.x;
   const int l = (int)(idx % L);
   const long long hp = idx / L;
-  const bool live = hp < (long long)H * P;  // a dead lane still takes part in the shuffles of its warp
-  const int h = live ? (int)(hp / P) : 0, p = live ? (int)(hp % P) : 0;
+  const bool live = hp < (long long)H * PC;  // a dead lane still takes part in the shuffles of its warp
+  const int h = live ? (int)(hp / PC) : 0, p0 = live ? (int)(hp % PC) * PP : 0;
   const int slot = slot_ids[b];
-  const int t0 = q_start[b], t1 = q_start[b + 1];
   const int inner = H * P;
   if (slot < 0 || slot >= num_slots) {
     if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
-    if (live && l == 0)
-      for (int t = t0; t < t1; ++t) y[(size_t)t * inner + hp] = 0.f;
+    if (MODE != 1 && live && l == 0)
+      for (int t = t0; t < t1; ++t)
+        for (int c = 0; c < PP; ++c) y[(size_t)t * inner + h * P + p0 + c] = 0.f;
     return;
   }
   const int g = h / (H / G);
   const int n0 = l * SSD_PER;
-  float S[SSD_PER];
-  float* st = state + (((size_t)slot * H + h) * N) * P + p;
+  const int states = max(0, min(SSD_PER, N - n0));
+  float S[PP][SSD_PER];
+  float* st = (MODE == 0 ? state + ((size_t)slot * H + h) * N * P : scratch + record + (size_t)h * N * P) + p0;
 #pragma unroll
-  for (int i = 0; i < SSD_PER; ++i) S[i] = (live && n0 + i < N) ? st[(size_t)(n0 + i) * P] : 0.f;
-  const float rate = -expf(A_log[h]), db = dt_bias[h], dskip = Dp[h];
-  const int b_col = inner + g * N + n0, c_col = inner + G * N + g * N + n0;
+  for (int c = 0; c < PP; ++c)
+#pragma unroll
+    for (int i = 0; i < SSD_PER; ++i) S[c][i] = (MODE != 1 && live && i < states) ? st[(size_t)(n0 + i) * P + c] : 0.f;
   constexpr bool exact = sizeof(T) == 4;
+  const float rate = -expf(A_log[h]), db = dt_bias[h], dskip = Dp[h];
+  const int x_col = h * P + p0, b_col = inner + g * N + n0, c_col = inner + G * N + g * N + n0;
+  float log_total = 0.f;
   for (int t = t0; t < t1; ++t) {
     const T* row = xbc + (size_t)t * ld;
-    const float step = softplus_f(to_float(proj[(size_t)t * ld_proj + dt_col + h]) + db);
+    const float pre = to_float(proj[(size_t)t * ld_proj + dt_col + h]) + db;
+    const float step = exact ? softplus_f(pre) : fmaxf(pre, 0.f) + __logf(1.0f + __expf(-fabsf(pre)));
     const float log_a = rate * step;
-    const float a = expf(log_a);
-    const float x = to_float(row[hp < inner ? hp : 0]);
-    const float sx = step * x;
-    float part = 0.f;
+    const float a = exact ? expf(log_a) : __expf(log_a);
+    log_total += log_a;
+    float Bv[SSD_PER], Cv[SSD_PER], x[PP];
+    ssd_load16<T, VEC>(row, b_col, states, Bv);
+    if (MODE != 1) ssd_load16<T, VEC>(row, c_col, states, Cv);
 #pragma unroll
-    for (int i = 0; i < SSD_PER; ++i) {
-      if (n0 + i < N) {
-        S[i] = ssd_update(log_a, a, S[i], sx * to_float(row[b_col + i]), exact);
-        part = fmaf(S[i], to_float(row[c_col + i]), part);
+    for (int c = 0; c < PP; ++c) x[c] = to_float(row[x_col + c]);
+#pragma unroll
+    for (int c = 0; c < PP; ++c) {
+      const float sx = step * x[c];
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < SSD_PER; ++i) {
+        if (VEC || i < states) {
+          S[c][i] = ssd_update(log_a, a, S[c][i], sx * Bv[i], exact);
+          if (MODE != 1) part = fmaf(S[c][i], Cv[i], part);
+        }
+      }
+      if (MODE != 1) {
+        for (int o = L >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (live && l == 0) y[(size_t)t * inner + x_col + c] = fmaf(dskip, x[c], part);
       }
     }
-    for (int o = L >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    if (live && l == 0) y[(size_t)t * inner + hp] = fmaf(dskip, x, part);
   }
-  if (live) {
+  if (MODE == 2 || !live) return;
+#pragma unroll
+  for (int c = 0; c < PP; ++c)
 #pragma unroll
     for (int i = 0; i < SSD_PER; ++i)
-      if (n0 + i < N) st[(size_t)(n0 + i) * P] = S[i];
+      if (i < states) st[(size_t)(n0 + i) * P + c] = S[c][i];
+  if (MODE == 1 && l == 0 && p0 == 0) scratch[record + (size_t)H * N * P + h] = __expf(log_total);
+}
+
+// One thread per state value of a request: chunk after chunk, the record's "state reached from zero" is replaced by
+// the state the chunk starts from, S_in(j + 1) = product_j S_in(j) + reached_j; the last one goes to the slot.
+__global__ void ssd_carry_kernel(float* __restrict__ scratch, float* __restrict__ state, const int* __restrict__ q_start,
+                                 const int* __restrict__ slot_ids, int H, int N, int P, int num_slots) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x;
+  const size_t e = (size_t)blockIdx.y * blockDim.x + threadIdx.x, per_head = (size_t)N * P, all = (size_t)H * per_head;
+  const int slot = slot_ids[b];
+  if (e >= all || slot < 0 || slot >= num_slots) return;
+  const int t0 = q_start[b], chunks = (q_start[b + 1] - t0 + SSD_CHUNK - 1) / SSD_CHUNK;
+  const int h = (int)(e / per_head);
+  float S = state[(size_t)slot * all + e];
+  float* rec = scratch + (size_t)(t0 / SSD_CHUNK + b) * (all + H);
+  for (int j = 0; j < chunks; ++j, rec += all + H) {
+    const float reached = rec[e];
+    rec[e] = S;
+    S = fmaf(rec[all + h], S, reached);
   }
+  state[(size_t)slot * all + e] = S;
 }
 
 // One block per (token, part).  y: float32 [T, I]; z: [T, ld_z] at column z_col; out: [T, I].
@@ -113,23 +192,72 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
   else if ((dtype) == Q3_BF16) { using E = __nv_bfloat16; CALL; } \
   else return Q3_ERR_DTYPE;
 
-// xbc: [T, ld] in `dtype`; proj: [T, ld_proj] in `dtype` with dt at dt_col; state: float32 [num_slots, H, N, P];
-// y: float32 [T, H * P].
-extern "C" int q3_ssd_scan(const void* xbc, int ld, const void* proj, int ld_proj, int dt_col, const float* dt_bias,
-                           const float* A_log, const float* Dp, float* state, const int* q_start, const int* slot_ids,
-                           float* y, int dtype, int T, int B, int H, int P, int N, int G, int num_slots, int* status,
-                           cudaStream_t stream) {
-  if (T <= 0 || B <= 0) return 0;
-  if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G || N > 32 * q3::SSD_PER) return Q3_ERR_SIZE;
+namespace q3 {
+
+template <typename T, int PP, bool VEC>
+static int ssd_launch(const void* xbc, int ld, const void* proj, int ld_proj, int dt_col, const float* dt_bias,
+                      const float* A_log, const float* Dp, float* state, float* scratch, const int* q_start,
+                      const int* slot_ids, float* y, int B, int max_q_len, int H, int P, int N, int G, int num_slots,
+                      int* status, cudaStream_t stream) {
   int L = 1;
-  while (L * q3::SSD_PER < N) L <<= 1;
-  const long long threads = (long long)H * P * L;
+  while (L * SSD_PER < N) L <<= 1;
+  const long long threads = (long long)H * (P / PP) * L;
   const long long blocks = (threads + 127) / 128;
   if (blocks > 65535) return Q3_ERR_SIZE;
-  Q3_BY_DTYPE(dtype, q3::launch(q3::ssd_scan_kernel<E>, dim3(B, (unsigned)blocks), dim3(128), 0, stream, (const E*)xbc, ld,
-                                (const E*)proj, ld_proj, dt_col, dt_bias, A_log, Dp, state, q_start, slot_ids, y, H, P, N,
-                                G, L, num_slots, status))
-  return q3::launch_status();
+  const T* x = (const T*)xbc;
+  const T* pr = (const T*)proj;
+  if (!scratch) {
+    launch(ssd_scan_kernel<T, PP, VEC, 0>, dim3(B, (unsigned)blocks), dim3(128), 0, stream, x, ld, pr, ld_proj, dt_col,
+           dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, status);
+    return launch_status();
+  }
+  const int chunks = (max_q_len + SSD_CHUNK - 1) / SSD_CHUNK;
+  if (chunks > 65535) return Q3_ERR_SIZE;
+  const size_t all = (size_t)H * N * P;
+  if ((all + 255) / 256 > 65535) return Q3_ERR_SIZE;
+  launch(ssd_scan_kernel<T, PP, VEC, 1>, dim3(B, (unsigned)blocks, chunks), dim3(128), 0, stream, x, ld, pr, ld_proj,
+         dt_col, dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, status);
+  launch(ssd_carry_kernel, dim3(B, (unsigned)((all + 255) / 256)), dim3(256), 0, stream, scratch, state, q_start, slot_ids,
+         H, N, P, num_slots);
+  launch(ssd_scan_kernel<T, PP, VEC, 2>, dim3(B, (unsigned)blocks, chunks), dim3(128), 0, stream, x, ld, pr, ld_proj,
+         dt_col, dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, status);
+  return launch_status();
+}
+
+}  // namespace q3
+
+extern "C" int q3_ssd_chunk() { return q3::SSD_CHUNK; }
+
+// xbc: [T, ld] in `dtype`; proj: [T, ld_proj] in `dtype` with dt at dt_col; state: float32 [num_slots, H, N, P];
+// y: float32 [T, H * P].  With `scratch` (float32, (T / chunk + B + 1) records of H * N * P + H floats; bfloat16 only)
+// the portions run in chunks of q3_ssd_chunk() tokens side by side: three launches.
+extern "C" int q3_ssd_scan(const void* xbc, int ld, const void* proj, int ld_proj, int dt_col, const float* dt_bias,
+                           const float* A_log, const float* Dp, float* state, float* scratch, const int* q_start,
+                           const int* slot_ids, float* y, int dtype, int T, int B, int max_q_len, int H, int P, int N,
+                           int G, int num_slots, int* status, cudaStream_t stream) {
+  if (T <= 0 || B <= 0) return 0;
+  if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G || N > 32 * q3::SSD_PER) return Q3_ERR_SIZE;
+  if (dtype == Q3_F32) {
+    if (scratch) return Q3_ERR_DTYPE;  // the float32 run walks a portion in one piece, whatever its cut
+    if (P % 4 == 0)
+      return q3::ssd_launch<float, 4, false>(xbc, ld, proj, ld_proj, dt_col, dt_bias, A_log, Dp, state, nullptr, q_start,
+                                             slot_ids, y, B, max_q_len, H, P, N, G, num_slots, status, stream);
+    return q3::ssd_launch<float, 1, false>(xbc, ld, proj, ld_proj, dt_col, dt_bias, A_log, Dp, state, nullptr, q_start,
+                                           slot_ids, y, B, max_q_len, H, P, N, G, num_slots, status, stream);
+  }
+  if (dtype != Q3_BF16) return Q3_ERR_DTYPE;
+  using bf16 = __nv_bfloat16;
+  const bool vec = N % 16 == 0 && (H * P) % 8 == 0 && ld % 8 == 0 && (uintptr_t)xbc % 16 == 0;
+#define Q3_SSD(PP, VEC)                                                                                                  \
+  return q3::ssd_launch<bf16, PP, VEC>(xbc, ld, proj, ld_proj, dt_col, dt_bias, A_log, Dp, state, scratch, q_start,      \
+                                       slot_ids, y, B, max_q_len, H, P, N, G, num_slots, status, stream);
+  if (P % 4 == 0) {
+    if (vec) { Q3_SSD(4, true) }
+    Q3_SSD(4, false)
+  }
+  if (vec) { Q3_SSD(1, true) }
+  Q3_SSD(1, false)
+#undef Q3_SSD
 }
 
 extern "C" int q3_gated_group_norm(const float* y, const void* z, int ld_z, int z_col, const float* weight, void* out,

@@ -134,8 +134,8 @@ _SIGNATURES = {
                            _c_void_p, _c_void_p],
     "q3_gate_heads": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_ssd_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-                    _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
-                    _c_void_p],
+                    _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                    _c_int, _c_void_p, _c_void_p],
     "q3_gated_group_norm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                             _c_float, _c_void_p],
 }
@@ -169,6 +169,8 @@ def library() -> ctypes.CDLL:
                 lib.q3_attn_decode_blocks_per_sm.restype = _c_int
                 lib.q3_latent_attn_mma_takes.argtypes = [_c_int, _c_int]
                 lib.q3_latent_attn_mma_takes.restype = _c_int
+                lib.q3_ssd_chunk.argtypes = []
+                lib.q3_ssd_chunk.restype = _c_int
                 lib.q3_scan_chunk.argtypes = []
                 lib.q3_scan_chunk.restype = _c_int
                 lib.q3_sample_scratch_bytes.argtypes = [_c_int]
@@ -1471,12 +1473,33 @@ def gate_heads(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------ state-space recurrence with a decay per head
+def ssd_chunk() -> int:
+    """Tokens per chunk of the chunked state-space scan."""
+    if "ssd chunk" not in _DEVICE_FACTS:
+        _DEVICE_FACTS["ssd chunk"] = int(library()._lib.q3_ssd_chunk())
+    return _DEVICE_FACTS["ssd chunk"]
+
+
+def ssd_scratch_numel(num_tokens: int, num_seqs: int, heads: int, vdim: int, n_state: int) -> int:
+    """Floats of scratch that the chunked form needs for a step of so many tokens and requests."""
+    return (num_tokens // ssd_chunk() + num_seqs + 1) * (heads * n_state * vdim + heads)
+
+
+def ssd_chunked_pays(dtype: torch.dtype, max_q_len: int) -> bool:
+    """bfloat16 with a portion of at least four chunks: the portions run in chunks side by side.  The float32 run
+    walks every portion in one piece, so that its bits do not depend on how a prompt was cut."""
+    return dtype == torch.bfloat16 and max_q_len >= 4 * ssd_chunk()
+
+
 def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
              d_skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int,
-             y: torch.Tensor, heads: int, vdim: int, n_state: int, groups: int, status: torch.Tensor) -> None:
+             y: torch.Tensor, heads: int, vdim: int, n_state: int, groups: int, status: torch.Tensor,
+             max_q_len: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
     """Per head h (group g = h // (heads / groups)): step = softplus(dt + dt_bias[h]); S <- exp(-exp(a_log[h]) step) S
     + step B_g x_h^T; y_h = S^T C_g + d_skip[h] x_h.  xbc [T, ld]: x (heads * vdim columns), then B and C (groups *
-    n_state each); dt: proj[:, dt_col + h]; state float32 [slots, heads, n_state, vdim]; y float32 [T, heads * vdim]."""
+    n_state each); dt: proj[:, dt_col + h]; state float32 [slots, heads, n_state, vdim]; y float32 [T, heads * vdim].
+    With ``scratch`` (``ssd_scratch_numel`` floats) and a longest portion ``max_q_len`` of ``ssd_chunked_pays`` the
+    portions are cut into chunks that run side by side."""
     _check("ssd_scan.xbc", xbc)
     _check("ssd_scan.proj", proj, xbc.dtype)
     _check("ssd_scan.y", y, torch.float32)
@@ -1492,10 +1515,16 @@ def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.
             or q_start.numel() < num_seqs + 1):
         raise KernelError(f"ssd_scan: xbc {tuple(xbc.shape)}, proj {tuple(proj.shape)}, y {tuple(y.shape)}, state "
                           f"{tuple(state.shape)}")
+    chunked = scratch is not None and ssd_chunked_pays(xbc.dtype, max_q_len)
+    if chunked:
+        _check("ssd_scan.scratch", scratch, torch.float32)
+        if scratch.numel() < ssd_scratch_numel(T, num_seqs, heads, vdim, n_state):
+            raise KernelError(f"ssd_scan: scratch of {scratch.numel()} floats for {T} tokens of {num_seqs} requests")
     code = library().q3_ssd_scan(xbc.data_ptr(), ld, proj.data_ptr(), proj.shape[1], int(dt_col), dt_bias.data_ptr(),
-                                 a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), q_start.data_ptr(),
-                                 slot_ids.data_ptr(), y.data_ptr(), dtype_tag(xbc.dtype), T, int(num_seqs), heads, vdim,
-                                 n_state, groups, state.shape[0], status.data_ptr(), _stream())
+                                 a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), _ptr(scratch) if chunked else None,
+                                 q_start.data_ptr(), slot_ids.data_ptr(), y.data_ptr(), dtype_tag(xbc.dtype), T,
+                                 int(num_seqs), int(max_q_len), heads, vdim, n_state, groups, state.shape[0],
+                                 status.data_ptr(), _stream())
     _done("ssd_scan", code, f"heads {heads} x {vdim}, state {n_state}, groups {groups}")
 
 

@@ -233,6 +233,10 @@ class SSD(Mixer, _NamedTensors):
         self._xbc = rt.shared("ssd.xbc", rt.max_tokens, self.channels)
         self._y = rt.shared("ssd.y", rt.max_tokens, self.inner, dtype=torch.float32)
         self._gated = rt.shared("ssd.gated", rt.max_tokens, self.inner)
+        self._chunks = None
+        if rt.dtype == torch.bfloat16 and ops.ssd_chunked_pays(rt.dtype, rt.max_tokens):
+            self._chunks = rt.shared("ssd.chunks", ops.ssd_scratch_numel(rt.max_tokens, rt.max_seqs, self.num_heads,
+                                                                         self.vdim, self.state_size), dtype=torch.float32)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         T, inner = x.shape[0], self.inner
@@ -244,7 +248,7 @@ class SSD(Mixer, _NamedTensors):
         y = self._y[:T]
         ops.ssd_scan(xbc, proj, inner + self.channels, self.dt_bias, self.a_log, self.d_skip, ctx.state(cache_id, "state"),
                      ctx.q_start, ctx.slot_ids, ctx.num_seqs, y, self.num_heads, self.vdim, self.state_size, self.groups,
-                     status)
+                     status, max_q_len=ctx.max_q_len, scratch=self._chunks)
         gated = self._gated[:T]
         ops.gated_group_norm(y, proj, 0, self.norm_weight, gated, self.norm_groups, self.norm_eps)
         return self.out_proj(gated)

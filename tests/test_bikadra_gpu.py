@@ -189,6 +189,49 @@ def test_mixer_alone_whole_in_portions_and_beside_another_request(kind, dtype):
         close(torch.cat(got[r]), want[r], dtype, f"{kind} portions {r}")
 
 
+@pytest.mark.parametrize("kind", ["ssd", "ssd, wide state", "ssd, three lanes of states"])
+def test_long_portions_run_in_chunks_and_leave_the_same_state(kind):
+    """bfloat16: a portion of several hundred tokens is cut into chunks that run side by side, a short one is
+    walked in one piece; a long portion beside a single token of another request, then the same tokens in short
+    portions: the outputs agree with the plain implementation and the float32 states that the two ways leave agree
+    to float32 rounding."""
+    from qwen3_from_scratch_b200.kernels import ops
+    from qwen3_from_scratch_b200.parts.base import PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    table = mixers()
+    # a state of 48: four lanes of which the last holds nothing; channels and states in multiples of 8 and 16 (the
+    # form with 16-byte loads)
+    table["ssd, three lanes of states"] = ({"hidden_size": 40, "num_heads": 4, "vdim": 16, "state": 48, "groups": 2,
+                                            "norm_groups": 2, "conv": 4, "norm_eps": 1e-5},)
+    params = table[kind][0]
+    bench = MixerBench(create_part("mixer", PartSpec("ssd", params), name="m"), "bfloat16", max_tokens=1024, pages=8, seed=13)
+    g = torch.Generator().manual_seed(14)
+    x_of = {"a": torch.randn(700, 40, generator=g).to(torch.bfloat16), "b": torch.randn(3, 40, generator=g).to(torch.bfloat16)}
+    fn = _ssd(params)
+    want = {r: fn(x.double(), bench.ref, None)[0] for r, x in x_of.items()}
+    with plain.bfloat16_projections():  # what rounding alone does over 700 tokens: the bound is three times that
+        rounded = fn(x_of["a"].double(), bench.ref, None)[0]
+    tol = max(TOL["bfloat16"], 3 * float((rounded - want["a"]).abs().max()) / float(want["a"].abs().max()))
+    call = lambda x, ctx: bench.part.forward(x.cuda().contiguous(), ctx, 0, True)  # noqa: E731
+    assert ops.ssd_chunked_pays(torch.bfloat16, 697) and not ops.ssd_chunked_pays(torch.bfloat16, 100)
+    states = []
+    for steps in ([[("b", 2)], [("a", 697), ("b", 1)], [("a", 3)]],
+                  [[("b", 2)]] + [[("a", 100)]] * 3 + [[("a", 100), ("b", 1)]] + [[("a", 100)]] * 3):
+        got = {r: [] for r in x_of}
+        for step in steps:
+            for r, y in bench.run(step, x_of, call).items():
+                got[r].append(y)
+        for r in x_of:
+            close(torch.cat(got[r]), want[r], "bfloat16", f"{kind} {r}", tol=tol)
+        slot = bench.manager.slot("a")
+        states.append({k: t[slot].clone() for k, t in bench.storage.states.items()})
+        bench.manager.close("a")
+        bench.manager.close("b")
+    for k in states[0]:
+        scale = float(states[0][k].abs().max())
+        assert float((states[0][k] - states[1][k]).abs().max()) <= 2e-5 * scale, k
+
+
 @pytest.mark.parametrize("dtype", list(DT))
 def test_sharp_attention_reads_keys_far_back_and_at_page_borders(dtype):
     """A scale so large that nearly every query gives all its weight to one key, which random weights put
