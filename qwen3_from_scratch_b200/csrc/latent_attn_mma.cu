@@ -20,22 +20,27 @@
 namespace q3 {
 
 constexpr int LM_KT = 32;  // keys per tile
-constexpr int LM_SP = LM_KT + 8;  // row pitch of the partial score tiles: eight rows of a warp's store fall on distinct banks
+
+__device__ __forceinline__ float lm_exp2(float x) {  // 2^x by the hardware's unit; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // KS: k-steps of 16 per warp in the scores (rank + rot padded to 64 * KS); NO: pairs of 8-column output tiles per
 // warp (rank = 64 * NO); RG: row groups per block.
 template <int KS, int NO, int RG>
-__global__ void __launch_bounds__(RG * 128)
+__global__ void __launch_bounds__(RG * 128, RG == 2 ? 2 : 4)
 latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ q_rot,
                        const __nv_bfloat16* __restrict__ c_pages, const __nv_bfloat16* __restrict__ r_pages,
                        const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ table,
                        int stride, int page_size, int num_pages, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ partial, int Ttot, int H, int rank, int rot, float scale_log2, int splits,
-                       int* status) {
+                       int page_shift, int* status) {
   constexpr int DKP = 64 * KS, PITCH = DKP + 8, BM = 16 * RG;
   extern __shared__ __align__(16) unsigned char lm_smem[];
   __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);                       // [2][LM_KT][PITCH]
-  float* sp = reinterpret_cast<float*>(lm_smem + (size_t)2 * LM_KT * PITCH * sizeof(__nv_bfloat16));  // [RG][4][16][LM_SP]
+  float* sp = reinterpret_cast<float*>(lm_smem + (size_t)2 * LM_KT * PITCH * sizeof(__nv_bfloat16));  // [RG][4 warps][LM_KT / 8][32 lanes] float4
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, split = blockIdx.z;
@@ -92,22 +97,25 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
   // LM_KT keys by RG * 128 threads: a key's row is copied by TPK threads, which look its page up once
   constexpr int TPK = RG * 128 / LM_KT, CHUNKS = DKP / 8;
   const int load_j = threadIdx.x / TPK, load_c = threadIdx.x % TPK;
-  auto load_tile = [&](int tile, int stage) {
+  // the page of this thread's key in a tile (-1: a hole or a bad id, -2: past the block's keys); asked for one tile
+  // before the copy that needs it, so that the table's answer is there when the copy is issued
+  auto page_of = [&](int tile) {
+    const int n = tile * LM_KT + load_j;
+    return n < keys ? table_page(trow, page_shift >= 0 ? n >> page_shift : n / page_size, stride, status) : -2;
+  };
+  auto load_tile = [&](int tile, int stage, int page) {
     __nv_bfloat16* dst = k_s + ((size_t)stage * LM_KT + load_j) * PITCH;
     const int n = tile * LM_KT + load_j;
     const __nv_bfloat16* c_src = c_pages;
     const __nv_bfloat16* r_src = r_pages;
     bool ok = false;
-    if (n < keys) {
-      const int page = table_page(trow, n / page_size, stride, status);
-      if (page >= 0 && page < num_pages) {
-        const size_t slot = (size_t)page * page_size + n % page_size;
-        c_src = c_pages + slot * rank;
-        r_src = r_pages + slot * rot;
-        ok = true;
-      } else if (load_c == 0) {
-        atomicOr(status, Q3_STATUS_BAD_PAGE);
-      }
+    if (page >= 0 && page < num_pages) {
+      const size_t slot = (size_t)page * page_size + (page_shift >= 0 ? n & (page_size - 1) : n % page_size);
+      c_src = c_pages + slot * rank;
+      r_src = r_pages + slot * rot;
+      ok = true;
+    } else if (page != -2 && load_c == 0) {
+      atomicOr(status, Q3_STATUS_BAD_PAGE);
     }
 #pragma unroll
     for (int c = load_c; c < CHUNKS; c += TPK) {
@@ -122,11 +130,13 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
   for (int i = 0; i < 2 * NO; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  if (tile_lo < tile_hi) load_tile(tile_lo, 0);
+  if (tile_lo < tile_hi) load_tile(tile_lo, 0, page_of(tile_lo));
   cp_async_commit();
+  int page_next = tile_lo + 1 < tile_hi ? page_of(tile_lo + 1) : -2;
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int stage = (tile - tile_lo) & 1;
-    if (tile + 1 < tile_hi) load_tile(tile + 1, stage ^ 1);
+    if (tile + 1 < tile_hi) load_tile(tile + 1, stage ^ 1, page_next);
+    if (tile + 2 < tile_hi) page_next = page_of(tile + 2);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -146,31 +156,32 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
         mma_bf16(s[2 * np + 1], qa[ks], kb[2], kb[3]);
       }
     }
-    float* mine = sp + ((size_t)(rg * 4 + w) * 16) * LM_SP;
+    // the four warps of a row group hold the same places of the tile in the same lanes: a lane leaves its fragment
+    // as whole float4s, [warp][n-tile][lane], and reads the other warps' at its own lane
+    float4* sp4 = reinterpret_cast<float4*>(sp) + (size_t)rg * 4 * (LM_KT / 8) * 32;
 #pragma unroll
     for (int nt = 0; nt < LM_KT / 8; ++nt)
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-        *reinterpret_cast<float2*>(mine + (gid + 8 * r) * LM_SP + nt * 8 + 2 * tid4) = make_float2(s[nt][2 * r], s[nt][2 * r + 1]);
+      sp4[(w * (LM_KT / 8) + nt) * 32 + lane] = make_float4(s[nt][0], s[nt][1], s[nt][2], s[nt][3]);
     __syncthreads();
     // the whole tile's scores, summed in the order of the warps
-    const float* all = sp + ((size_t)rg * 4 * 16) * LM_SP;
     const int base_n = tile * LM_KT;
 #pragma unroll
-    for (int nt = 0; nt < LM_KT / 8; ++nt)
+    for (int nt = 0; nt < LM_KT / 8; ++nt) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int ww = 0; ww < 4; ++ww) {
-          const float2 v = *reinterpret_cast<const float2*>(all + ((size_t)ww * 16 + gid + 8 * r) * LM_SP + nt * 8 + 2 * tid4);
-          acc.x += v.x;
-          acc.y += v.y;
-        }
-        const int n = base_n + nt * 8 + 2 * tid4;
-        s[nt][2 * r] = n <= row_pos[r] ? acc.x * scale_log2 : -INFINITY;
-        s[nt][2 * r + 1] = n + 1 <= row_pos[r] ? acc.y * scale_log2 : -INFINITY;
+      for (int ww = 0; ww < 4; ++ww) {
+        const float4 v = sp4[(ww * (LM_KT / 8) + nt) * 32 + lane];
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
       }
+      const int n = base_n + nt * 8 + 2 * tid4;
+      s[nt][0] = n <= row_pos[0] ? acc.x * scale_log2 : -INFINITY;
+      s[nt][1] = n + 1 <= row_pos[0] ? acc.y * scale_log2 : -INFINITY;
+      s[nt][2] = n <= row_pos[1] ? acc.z * scale_log2 : -INFINITY;
+      s[nt][3] = n + 1 <= row_pos[1] ? acc.w * scale_log2 : -INFINITY;
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       float mx = -INFINITY;
@@ -180,17 +191,20 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m[r], mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m[r] - m_use);
+      const float alpha = lm_exp2(m[r] - m_use);
+      const bool grew = m_new != m[r];
       m[r] = m_new;
       l[r] *= alpha;
+      if (__any_sync(0xffffffffu, grew)) {  // most tiles leave every row's maximum where it was
 #pragma unroll
-      for (int i = 0; i < 2 * NO; ++i) {
-        o[i][2 * r] *= alpha;
-        o[i][2 * r + 1] *= alpha;
+        for (int i = 0; i < 2 * NO; ++i) {
+          o[i][2 * r] *= alpha;
+          o[i][2 * r + 1] *= alpha;
+        }
       }
 #pragma unroll
       for (int nt = 0; nt < LM_KT / 8; ++nt) {
-        const float p0 = exp2f(s[nt][2 * r] - m_use), p1 = exp2f(s[nt][2 * r + 1] - m_use);
+        const float p0 = lm_exp2(s[nt][2 * r] - m_use), p1 = lm_exp2(s[nt][2 * r + 1] - m_use);
         s[nt][2 * r] = p0;
         s[nt][2 * r + 1] = p1;
         l[r] += p0 + p1;
@@ -273,7 +287,7 @@ static int lm_launch(const float* q_abs, const void* q_rot, const void* c_pages,
                      int* status, cudaStream_t stream) {
   using bf16 = __nv_bfloat16;
   constexpr int PITCH = 64 * KS + 8;
-  const size_t smem = (size_t)2 * LM_KT * PITCH * sizeof(bf16) + (size_t)RG * 4 * 16 * LM_SP * sizeof(float);
+  const size_t smem = (size_t)2 * LM_KT * PITCH * sizeof(bf16) + (size_t)RG * 4 * 16 * LM_KT * sizeof(float);
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(latent_attn_mma_kernel<KS, NO, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -283,7 +297,8 @@ static int lm_launch(const float* q_abs, const void* q_rot, const void* c_pages,
   if (tiles > 65535 || splits > 65535) return Q3_ERR_SIZE;
   launch(latent_attn_mma_kernel<KS, NO, RG>, dim3(B, (unsigned)tiles, splits), dim3(RG * 128), smem, stream, q_abs,
          (const bf16*)q_rot, (const bf16*)c_pages, (const bf16*)r_pages, q_start, kv_len, table, stride, page_size,
-         num_pages, (bf16*)out, partial, T, H, rank, rot, scale * 1.4426950408889634f, splits, status);
+         num_pages, (bf16*)out, partial, T, H, rank, rot, scale * 1.4426950408889634f, splits, page_shift_of(page_size),
+         status);
   if (splits > 1) {
     g_launch_early = false;  // started after every range has left its result
     launch(latent_attn_merge_kernel, dim3((unsigned)((size_t)T * H)), dim3(128), 0, stream, (const float*)partial,
