@@ -119,6 +119,132 @@ __global__ void hc_norm_kernel(float* __restrict__ xs, HcPending pend, const flo
   }
 }
 
+// The same with four features per access and the row's u kept in registers: W a multiple of 4, at most
+// 4 * VPT * blockDim.x; every pointer 16-byte aligned (the output 8-byte for bfloat16).
+template <typename T>
+__device__ __forceinline__ float4 hc_load4(const T* p);
+template <>
+__device__ __forceinline__ float4 hc_load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 hc_load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                     __uint_as_float(v.y & 0xffff0000u));
+}
+__device__ __forceinline__ void hc_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void hc_store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
+template <typename T, bool ROWS, int VPT>
+__global__ void hc_norm_vec_kernel(float* __restrict__ xs, HcPending pend, const float* __restrict__ read,
+                                   const float* __restrict__ weight, const int* __restrict__ rows, T* __restrict__ out,
+                                   int T_total, int S, int W, float eps, int* status) {
+  __shared__ float red[32];
+  __shared__ float s_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], s_write[HC_MAX_STREAMS], s_read[HC_MAX_STREAMS];
+  pdl_wait();
+  pdl_launch_dependents();
+  int t = blockIdx.x;
+  const int W4 = W >> 2;
+  T* o = out + (size_t)blockIdx.x * W;
+  if (ROWS) {
+    t = rows[blockIdx.x];
+    if (t < 0 || t >= T_total) {
+      if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+      for (int f = threadIdx.x; f < W4; f += blockDim.x) hc_store4(o + 4 * f, make_float4(0.f, 0.f, 0.f, 0.f));
+      return;
+    }
+  }
+  const bool open = pend.delta != nullptr;
+  if (threadIdx.x < S * S) s_mix[threadIdx.x] = open ? pend.mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    s_write[threadIdx.x] = open ? pend.write[threadIdx.x] : 0.f;
+    s_read[threadIdx.x] = ROWS ? 1.f : read[threadIdx.x];
+  }
+  __syncthreads();
+  float* x = xs + (size_t)t * S * W;
+  const T* delta = open ? (const T*)pend.delta + (size_t)t * W : nullptr;
+  float4 u[VPT];
+  float sumsq = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int f = threadIdx.x + k * blockDim.x;
+    u[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (f >= W4) continue;
+    float4 old[HC_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+      if (s < S) old[s] = *reinterpret_cast<const float4*>(x + (size_t)s * W + 4 * f);
+    if (open) {
+      const float4 y = hc_load4<T>(delta + 4 * f);
+#pragma unroll
+      for (int to = 0; to < HC_MAX_STREAMS; ++to) {
+        if (to < S) {
+          const float wr = s_write[to];
+          float4 v = make_float4(wr * y.x, wr * y.y, wr * y.z, wr * y.w);
+#pragma unroll
+          for (int from = 0; from < HC_MAX_STREAMS; ++from)
+            if (from < S) {
+              const float mx = s_mix[from * S + to];
+              v.x = fmaf(mx, old[from].x, v.x);
+              v.y = fmaf(mx, old[from].y, v.y);
+              v.z = fmaf(mx, old[from].z, v.z);
+              v.w = fmaf(mx, old[from].w, v.w);
+            }
+          if (!ROWS) *reinterpret_cast<float4*>(x + (size_t)to * W + 4 * f) = v;
+          const float rd = s_read[to];
+          u[k].x = fmaf(rd, v.x, u[k].x);
+          u[k].y = fmaf(rd, v.y, u[k].y);
+          u[k].z = fmaf(rd, v.z, u[k].z);
+          u[k].w = fmaf(rd, v.w, u[k].w);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int s = 0; s < HC_MAX_STREAMS; ++s)
+        if (s < S) {
+          const float rd = s_read[s];
+          u[k].x = fmaf(rd, old[s].x, u[k].x);
+          u[k].y = fmaf(rd, old[s].y, u[k].y);
+          u[k].z = fmaf(rd, old[s].z, u[k].z);
+          u[k].w = fmaf(rd, old[s].w, u[k].w);
+        }
+    }
+    sumsq = fmaf(u[k].x, u[k].x, fmaf(u[k].y, u[k].y, fmaf(u[k].z, u[k].z, fmaf(u[k].w, u[k].w, sumsq))));
+  }
+  const float rstd = rsqrtf(block_sum(sumsq, red) / (float)W + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int f = threadIdx.x + k * blockDim.x;
+    if (f >= W4) continue;
+    const float4 wv = *reinterpret_cast<const float4*>(weight + 4 * f);
+    hc_store4(o + 4 * f, make_float4(u[k].x * rstd * wv.x, u[k].y * rstd * wv.y, u[k].z * rstd * wv.z, u[k].w * rstd * wv.w));
+  }
+}
+
+template <typename T, bool ROWS>
+static bool hc_launch_vec(float* xs, HcPending pend, const float* read, const float* weight, const int* rows, void* out,
+                          int blocks, int T_total, int S, int W, float eps, int* status, cudaStream_t stream) {
+  if (W % 4 || (uintptr_t)xs % 16 || (uintptr_t)weight % 16 || (uintptr_t)out % 16 || (pend.delta && (uintptr_t)pend.delta % 16))
+    return false;
+  const int W4 = W / 4;
+  if (W4 > 256 * 4) return false;
+  int threads = W4 <= 256 ? ((W4 + 31) / 32) * 32 : 256;
+  if (threads < 64) threads = 64;
+  const int vpt = (W4 + threads - 1) / threads;
+  if (vpt == 1)
+    launch(hc_norm_vec_kernel<T, ROWS, 1>, dim3(blocks), dim3(threads), 0, stream, xs, pend, read, weight, rows, (T*)out,
+           T_total, S, W, eps, status);
+  else if (vpt == 2)
+    launch(hc_norm_vec_kernel<T, ROWS, 2>, dim3(blocks), dim3(threads), 0, stream, xs, pend, read, weight, rows, (T*)out,
+           T_total, S, W, eps, status);
+  else
+    launch(hc_norm_vec_kernel<T, ROWS, 4>, dim3(blocks), dim3(threads), 0, stream, xs, pend, read, weight, rows, (T*)out,
+           T_total, S, W, eps, status);
+  return true;
+}
+
 // logits <- cap * tanh(logits / cap), in place, float32.
 __global__ void softcap_kernel(float* __restrict__ logits, size_t total, float cap) {
   pdl_wait();
@@ -158,8 +284,11 @@ extern "C" int q3_hc_norm(float* xs, const void* delta, const float* mix, const 
   if (threads > 256) threads = 256;
   if (threads < 64) threads = 64;  // the first S * S threads fetch the mixing matrix
   q3::HcPending pend{delta, mix, write};
-  Q3_BY_DTYPE(dtype, q3::launch(q3::hc_norm_kernel<E, false>, dim3(T), dim3(threads), 0, stream, xs, pend, read, weight,
-                                (const int*)nullptr, (E*)out, T, S, W, eps, status))
+  Q3_BY_DTYPE(dtype, {
+    if (!q3::hc_launch_vec<E, false>(xs, pend, read, weight, nullptr, out, T, T, S, W, eps, status, stream))
+      q3::launch(q3::hc_norm_kernel<E, false>, dim3(T), dim3(threads), 0, stream, xs, pend, read, weight,
+                 (const int*)nullptr, (E*)out, T, S, W, eps, status);
+  })
   if (delta) q3::note_stream_written();
   return q3::launch_status();
 }
@@ -175,8 +304,11 @@ extern "C" int q3_hc_sum_norm_rows(const float* xs, const void* delta, const flo
   if (threads > 256) threads = 256;
   if (threads < 64) threads = 64;
   q3::HcPending pend{delta, mix, write};
-  Q3_BY_DTYPE(dtype, q3::launch(q3::hc_norm_kernel<E, true>, dim3(R), dim3(threads), 0, stream, (float*)xs, pend,
-                                (const float*)nullptr, weight, rows, (E*)out, T, S, W, eps, status))
+  Q3_BY_DTYPE(dtype, {
+    if (!q3::hc_launch_vec<E, true>((float*)xs, pend, nullptr, weight, rows, out, R, T, S, W, eps, status, stream))
+      q3::launch(q3::hc_norm_kernel<E, true>, dim3(R), dim3(threads), 0, stream, (float*)xs, pend, (const float*)nullptr,
+                 weight, rows, (E*)out, T, S, W, eps, status);
+  })
   return q3::launch_status();
 }
 

@@ -53,22 +53,24 @@ __device__ __forceinline__ void ssd_load16(const T* __restrict__ row, int col, i
 // A group of L lanes (a power of two, 16 states each) per (head, PP channels).  MODE 0: a request's whole portion from
 // its slot's state, which is renewed.  MODE 1 (blockIdx.z = chunk): the chunk from a zero state; leaves the state it
 // reaches and the product of its decays in `scratch`.  MODE 2: the chunk from the state that the carry left in
-// `scratch`; writes y.  A record of `scratch` is H * N * P + H floats; chunk j of request b is record
-// q_start[b] / SSD_CHUNK + b + j.
+// `scratch`; writes y.  A record of `scratch` holds every thread's 16 * PP state values side by side, in the order of
+// the threads (so that a chunk's state comes and goes in 16-byte pieces of whole lines), then H decay products
+// (padded to a multiple of four):
+// `record_floats` floats; chunk j of request b is record q_start[b] / SSD_CHUNK + b + j.
 template <typename T, int PP, bool VEC, int MODE>
 __global__ void __launch_bounds__(128)
 ssd_scan_kernel(const T* __restrict__ xbc, int ld, const T* __restrict__ proj, int ld_proj, int dt_col,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dp,
                 float* __restrict__ state, float* __restrict__ scratch, const int* __restrict__ q_start,
                 const int* __restrict__ slot_ids, float* __restrict__ y, int H, int P, int N, int G, int L, int num_slots,
-                int* status) {
+                size_t record_floats, int* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x;
   int t0 = q_start[b], t1 = q_start[b + 1];
   size_t record = 0;
   if (MODE != 0) {
-    record = (size_t)(t0 / SSD_CHUNK + b + blockIdx.z) * ((size_t)H * N * P + H);
+    record = (size_t)(t0 / SSD_CHUNK + b + blockIdx.z) * record_floats;
     t0 += blockIdx.z * SSD_CHUNK;
     if (t0 >= t1) return;
     t1 = min(t1, t0 + SSD_CHUNK);
@@ -92,11 +94,24 @@ ssd_scan_kernel(const T* __restrict__ xbc, int ld, const T* __restrict__ proj, i
   const int n0 = l * SSD_PER;
   const int states = max(0, min(SSD_PER, N - n0));
   float S[PP][SSD_PER];
-  float* st = (MODE == 0 ? state + ((size_t)slot * H + h) * N * P : scratch + record + (size_t)h * N * P) + p0;
+  float* st = state + ((size_t)slot * H + h) * N * P + p0;                       // MODE 0: the slot, [N, P] per head
+  float4* mine = reinterpret_cast<float4*>(scratch + record) + idx * (PP * SSD_PER / 4);  // else: this thread's piece
 #pragma unroll
   for (int c = 0; c < PP; ++c)
 #pragma unroll
-    for (int i = 0; i < SSD_PER; ++i) S[c][i] = (MODE != 1 && live && i < states) ? st[(size_t)(n0 + i) * P + c] : 0.f;
+    for (int i = 0; i < SSD_PER; ++i) S[c][i] = (MODE == 0 && live && i < states) ? st[(size_t)(n0 + i) * P + c] : 0.f;
+  if (MODE == 2 && live) {
+#pragma unroll
+    for (int c = 0; c < PP; ++c)
+#pragma unroll
+      for (int q = 0; q < SSD_PER / 4; ++q) {
+        const float4 v = mine[c * (SSD_PER / 4) + q];
+        S[c][4 * q] = v.x;
+        S[c][4 * q + 1] = v.y;
+        S[c][4 * q + 2] = v.z;
+        S[c][4 * q + 3] = v.w;
+      }
+  }
   constexpr bool exact = sizeof(T) == 4;
   const float rate = -expf(A_log[h]), db = dt_bias[h], dskip = Dp[h];
   const int x_col = h * P + p0, b_col = inner + g * N + n0, c_col = inner + G * N + g * N + n0;
@@ -131,34 +146,52 @@ ssd_scan_kernel(const T* __restrict__ xbc, int ld, const T* __restrict__ proj, i
     }
   }
   if (MODE == 2 || !live) return;
+  if (MODE == 1) {
+#pragma unroll
+    for (int c = 0; c < PP; ++c)
+#pragma unroll
+      for (int q = 0; q < SSD_PER / 4; ++q)
+        mine[c * (SSD_PER / 4) + q] = make_float4(S[c][4 * q], S[c][4 * q + 1], S[c][4 * q + 2], S[c][4 * q + 3]);
+    if (l == 0 && p0 == 0) scratch[record + record_floats - ((H + 3) & ~3) + h] = __expf(log_total);
+    return;
+  }
 #pragma unroll
   for (int c = 0; c < PP; ++c)
 #pragma unroll
     for (int i = 0; i < SSD_PER; ++i)
       if (i < states) st[(size_t)(n0 + i) * P + c] = S[c][i];
-  if (MODE == 1 && l == 0 && p0 == 0) scratch[record + (size_t)H * N * P + h] = __expf(log_total);
 }
 
-// One thread per state value of a request: chunk after chunk, the record's "state reached from zero" is replaced by
-// the state the chunk starts from, S_in(j + 1) = product_j S_in(j) + reached_j; the last one goes to the slot.
+// One thread per state value of a request, in the order of the records (thread of the scan, channel, state): chunk
+// after chunk, the record's "state reached from zero" is replaced by the state the chunk starts from,
+// S_in(j + 1) = product_j S_in(j) + reached_j; the last one goes to the slot.
 __global__ void ssd_carry_kernel(float* __restrict__ scratch, float* __restrict__ state, const int* __restrict__ q_start,
-                                 const int* __restrict__ slot_ids, int H, int N, int P, int num_slots) {
+                                 const int* __restrict__ slot_ids, int H, int N, int P, int PP, int L, int num_slots,
+                                 size_t record_floats) {
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x;
-  const size_t e = (size_t)blockIdx.y * blockDim.x + threadIdx.x, per_head = (size_t)N * P, all = (size_t)H * per_head;
+  const size_t e = (size_t)blockIdx.y * blockDim.x + threadIdx.x;
   const int slot = slot_ids[b];
-  if (e >= all || slot < 0 || slot >= num_slots) return;
+  const size_t decays_at = record_floats - ((H + 3) & ~3);
+  if (e >= decays_at || slot < 0 || slot >= num_slots) return;
+  const int PC = P / PP;
+  const size_t thread = e / (PP * SSD_PER);
+  const int within = (int)(e % (PP * SSD_PER)), c = within / SSD_PER, i = within % SSD_PER;
+  const int l = (int)(thread % L);
+  const size_t hp = thread / L;
+  const int h = (int)(hp / PC), n = l * SSD_PER + i, p = (int)(hp % PC) * PP + c;
+  if (n >= N) return;  // a lane's places beyond the last state
   const int t0 = q_start[b], chunks = (q_start[b + 1] - t0 + SSD_CHUNK - 1) / SSD_CHUNK;
-  const int h = (int)(e / per_head);
-  float S = state[(size_t)slot * all + e];
-  float* rec = scratch + (size_t)(t0 / SSD_CHUNK + b) * (all + H);
-  for (int j = 0; j < chunks; ++j, rec += all + H) {
+  float* home = state + (((size_t)slot * H + h) * N + n) * P + p;
+  float S = *home;
+  float* rec = scratch + (size_t)(t0 / SSD_CHUNK + b) * record_floats;
+  for (int j = 0; j < chunks; ++j, rec += record_floats) {
     const float reached = rec[e];
     rec[e] = S;
-    S = fmaf(rec[all + h], S, reached);
+    S = fmaf(rec[decays_at + h], S, reached);
   }
-  state[(size_t)slot * all + e] = S;
+  *home = S;
 }
 
 // One block per (token, part).  y: float32 [T, I]; z: [T, ld_z] at column z_col; out: [T, I].
@@ -208,19 +241,19 @@ static int ssd_launch(const void* xbc, int ld, const void* proj, int ld_proj, in
   const T* pr = (const T*)proj;
   if (!scratch) {
     launch(ssd_scan_kernel<T, PP, VEC, 0>, dim3(B, (unsigned)blocks), dim3(128), 0, stream, x, ld, pr, ld_proj, dt_col,
-           dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, status);
+           dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, (size_t)0, status);
     return launch_status();
   }
   const int chunks = (max_q_len + SSD_CHUNK - 1) / SSD_CHUNK;
   if (chunks > 65535) return Q3_ERR_SIZE;
-  const size_t all = (size_t)H * N * P;
-  if ((all + 255) / 256 > 65535) return Q3_ERR_SIZE;
+  const size_t all = (size_t)threads * PP * SSD_PER, record_floats = all + ((H + 3) & ~3);
+  if ((all + 255) / 256 > 65535 || record_floats % 4) return Q3_ERR_SIZE;
   launch(ssd_scan_kernel<T, PP, VEC, 1>, dim3(B, (unsigned)blocks, chunks), dim3(128), 0, stream, x, ld, pr, ld_proj,
-         dt_col, dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, status);
+         dt_col, dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, record_floats, status);
   launch(ssd_carry_kernel, dim3(B, (unsigned)((all + 255) / 256)), dim3(256), 0, stream, scratch, state, q_start, slot_ids,
-         H, N, P, num_slots);
+         H, N, P, PP, L, num_slots, record_floats);
   launch(ssd_scan_kernel<T, PP, VEC, 2>, dim3(B, (unsigned)blocks, chunks), dim3(128), 0, stream, x, ld, pr, ld_proj,
-         dt_col, dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, status);
+         dt_col, dt_bias, A_log, Dp, state, scratch, q_start, slot_ids, y, H, P, N, G, L, num_slots, record_floats, status);
   return launch_status();
 }
 
@@ -228,8 +261,16 @@ static int ssd_launch(const void* xbc, int ld, const void* proj, int ld_proj, in
 
 extern "C" int q3_ssd_chunk() { return q3::SSD_CHUNK; }
 
+// Floats of one record of the chunked form's scratch: 16 places per lane for every (head, channel), rounded up so that
+// a record starts on a 16-byte boundary, then the heads' decay products.
+extern "C" long long q3_ssd_record_floats(int H, int P, int N) {
+  int L = 1;
+  while (L * q3::SSD_PER < N) L <<= 1;
+  return (long long)H * P * L * q3::SSD_PER + ((H + 3) & ~3);
+}
+
 // xbc: [T, ld] in `dtype`; proj: [T, ld_proj] in `dtype` with dt at dt_col; state: float32 [num_slots, H, N, P];
-// y: float32 [T, H * P].  With `scratch` (float32, (T / chunk + B + 1) records of H * N * P + H floats; bfloat16 only)
+// y: float32 [T, H * P].  With `scratch` (float32, (T / chunk + B + 1) records of q3_ssd_record_floats; bfloat16 only)
 // the portions run in chunks of q3_ssd_chunk() tokens side by side: three launches.
 extern "C" int q3_ssd_scan(const void* xbc, int ld, const void* proj, int ld_proj, int dt_col, const float* dt_bias,
                            const float* A_log, const float* Dp, float* state, float* scratch, const int* q_start,

@@ -169,6 +169,8 @@ def library() -> ctypes.CDLL:
                 lib.q3_attn_decode_blocks_per_sm.restype = _c_int
                 lib.q3_latent_attn_mma_takes.argtypes = [_c_int, _c_int]
                 lib.q3_latent_attn_mma_takes.restype = _c_int
+                lib.q3_ssd_record_floats.argtypes = [_c_int, _c_int, _c_int]
+                lib.q3_ssd_record_floats.restype = _c_ll
                 lib.q3_ssd_chunk.argtypes = []
                 lib.q3_ssd_chunk.restype = _c_int
                 lib.q3_scan_chunk.argtypes = []
@@ -1482,7 +1484,7 @@ def ssd_chunk() -> int:
 
 def ssd_scratch_numel(num_tokens: int, num_seqs: int, heads: int, vdim: int, n_state: int) -> int:
     """Floats of scratch that the chunked form needs for a step of so many tokens and requests."""
-    return (num_tokens // ssd_chunk() + num_seqs + 1) * (heads * n_state * vdim + heads)
+    return (num_tokens // ssd_chunk() + num_seqs + 1) * int(library()._lib.q3_ssd_record_floats(heads, vdim, n_state))
 
 
 def ssd_chunked_pays(dtype: torch.dtype, max_q_len: int) -> bool:
