@@ -186,10 +186,20 @@ __global__ void ssd_carry_kernel(float* __restrict__ scratch, float* __restrict_
   float* home = state + (((size_t)slot * H + h) * N + n) * P + p;
   float S = *home;
   float* rec = scratch + (size_t)(t0 / SSD_CHUNK + b) * record_floats;
-  for (int j = 0; j < chunks; ++j, rec += record_floats) {
-    const float reached = rec[e];
-    rec[e] = S;
-    S = fmaf(rec[decays_at + h], S, reached);
+  for (int j0 = 0; j0 < chunks; j0 += 8, rec += 8 * record_floats) {  // eight chunks' loads in flight at a time
+    float reached[8], decay[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (j0 + k < chunks) {
+        reached[k] = rec[(size_t)k * record_floats + e];
+        decay[k] = rec[(size_t)k * record_floats + decays_at + h];
+      }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (j0 + k < chunks) {
+        rec[(size_t)k * record_floats + e] = S;
+        S = fmaf(decay[k], S, reached[k]);
+      }
   }
   *home = S;
 }

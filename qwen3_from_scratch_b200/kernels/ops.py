@@ -136,6 +136,9 @@ _SIGNATURES = {
     "q3_ssd_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                     _c_int, _c_void_p, _c_void_p],
+    "q3_ssd_scan_mma": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                        _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                        _c_void_p],
     "q3_gated_group_norm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                             _c_float, _c_void_p],
 }
@@ -171,6 +174,10 @@ def library() -> ctypes.CDLL:
                 lib.q3_latent_attn_mma_takes.restype = _c_int
                 lib.q3_ssd_record_floats.argtypes = [_c_int, _c_int, _c_int]
                 lib.q3_ssd_record_floats.restype = _c_ll
+                lib.q3_ssd_mma_takes.argtypes = [_c_int, _c_int]
+                lib.q3_ssd_mma_takes.restype = _c_int
+                lib.q3_ssd_mma_record_floats.argtypes = [_c_int, _c_int, _c_int]
+                lib.q3_ssd_mma_record_floats.restype = _c_ll
                 lib.q3_ssd_chunk.argtypes = []
                 lib.q3_ssd_chunk.restype = _c_int
                 lib.q3_scan_chunk.argtypes = []
@@ -1484,7 +1491,16 @@ def ssd_chunk() -> int:
 
 def ssd_scratch_numel(num_tokens: int, num_seqs: int, heads: int, vdim: int, n_state: int) -> int:
     """Floats of scratch that the chunked form needs for a step of so many tokens and requests."""
-    return (num_tokens // ssd_chunk() + num_seqs + 1) * int(library()._lib.q3_ssd_record_floats(heads, vdim, n_state))
+    record = int(library()._lib.q3_ssd_record_floats(heads, vdim, n_state))
+    if ssd_matrix_form(vdim, n_state):
+        record = max(record, int(library()._lib.q3_ssd_mma_record_floats(heads, vdim, n_state)))
+    return (num_tokens // ssd_chunk() + num_seqs + 1) * record
+
+
+def ssd_matrix_form(vdim: int, n_state: int) -> bool:
+    """Whether chunks of these sizes run as matrix products on the tensor cores (heads of 64 channels, a state of 64
+    or 128); other sizes walk their chunks token by token."""
+    return bool(library()._lib.q3_ssd_mma_takes(int(vdim), int(n_state)))
 
 
 def ssd_chunked_pays(dtype: torch.dtype, max_q_len: int) -> bool:
@@ -1496,12 +1512,13 @@ def ssd_chunked_pays(dtype: torch.dtype, max_q_len: int) -> bool:
 def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
              d_skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int,
              y: torch.Tensor, heads: int, vdim: int, n_state: int, groups: int, status: torch.Tensor,
-             max_q_len: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
+             max_q_len: int = 0, scratch: Optional[torch.Tensor] = None, kernel: str = "auto") -> None:
     """Per head h (group g = h // (heads / groups)): step = softplus(dt + dt_bias[h]); S <- exp(-exp(a_log[h]) step) S
     + step B_g x_h^T; y_h = S^T C_g + d_skip[h] x_h.  xbc [T, ld]: x (heads * vdim columns), then B and C (groups *
     n_state each); dt: proj[:, dt_col + h]; state float32 [slots, heads, n_state, vdim]; y float32 [T, heads * vdim].
     With ``scratch`` (``ssd_scratch_numel`` floats) and a longest portion ``max_q_len`` of ``ssd_chunked_pays`` the
-    portions are cut into chunks that run side by side."""
+    portions are cut into chunks that run side by side: as matrix products on the tensor cores where
+    ``ssd_matrix_form`` takes the sizes (``kernel="walk"`` keeps the token-by-token walk of the chunks)."""
     _check("ssd_scan.xbc", xbc)
     _check("ssd_scan.proj", proj, xbc.dtype)
     _check("ssd_scan.y", y, torch.float32)
@@ -1522,6 +1539,14 @@ def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.
         _check("ssd_scan.scratch", scratch, torch.float32)
         if scratch.numel() < ssd_scratch_numel(T, num_seqs, heads, vdim, n_state):
             raise KernelError(f"ssd_scan: scratch of {scratch.numel()} floats for {T} tokens of {num_seqs} requests")
+    if chunked and kernel != "walk" and ssd_matrix_form(vdim, n_state) and ld % 8 == 0:
+        code = library().q3_ssd_scan_mma(xbc.data_ptr(), ld, proj.data_ptr(), proj.shape[1], int(dt_col),
+                                         dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(),
+                                         scratch.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(), y.data_ptr(), T,
+                                         int(num_seqs), int(max_q_len), heads, vdim, n_state, groups, state.shape[0],
+                                         _stream())
+        _done("ssd_scan (matrix form)", code, f"heads {heads} x {vdim}, state {n_state}, groups {groups}")
+        return
     code = library().q3_ssd_scan(xbc.data_ptr(), ld, proj.data_ptr(), proj.shape[1], int(dt_col), dt_bias.data_ptr(),
                                  a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), _ptr(scratch) if chunked else None,
                                  q_start.data_ptr(), slot_ids.data_ptr(), y.data_ptr(), dtype_tag(xbc.dtype), T,

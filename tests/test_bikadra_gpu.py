@@ -189,7 +189,8 @@ def test_mixer_alone_whole_in_portions_and_beside_another_request(kind, dtype):
         close(torch.cat(got[r]), want[r], dtype, f"{kind} portions {r}")
 
 
-@pytest.mark.parametrize("kind", ["ssd", "ssd, wide state", "ssd, three lanes of states"])
+@pytest.mark.parametrize("kind", ["ssd", "ssd, wide state", "ssd, three lanes of states", "ssd, matrix form 64",
+                                  "ssd, matrix form 128"])
 def test_long_portions_run_in_chunks_and_leave_the_same_state(kind):
     """bfloat16: a portion of several hundred tokens is cut into chunks that run side by side, a short one is
     walked in one piece; a long portion beside a single token of another request, then the same tokens in short
@@ -203,7 +204,13 @@ def test_long_portions_run_in_chunks_and_leave_the_same_state(kind):
     # form with 16-byte loads)
     table["ssd, three lanes of states"] = ({"hidden_size": 40, "num_heads": 4, "vdim": 16, "state": 48, "groups": 2,
                                             "norm_groups": 2, "conv": 4, "norm_eps": 1e-5},)
+    # heads of 64 channels with a state of 64 or 128: the chunks run as matrix products on the tensor cores
+    table["ssd, matrix form 64"] = ({"hidden_size": 40, "num_heads": 4, "vdim": 64, "state": 64, "groups": 2,
+                                     "norm_groups": 4, "conv": 4, "norm_eps": 1e-5},)
+    table["ssd, matrix form 128"] = ({"hidden_size": 40, "num_heads": 2, "vdim": 64, "state": 128, "groups": 1,
+                                      "norm_groups": 1, "conv": 3, "norm_eps": 1e-5},)
     params = table[kind][0]
+    assert ops.ssd_matrix_form(params["vdim"], params["state"]) == ("matrix" in kind)
     bench = MixerBench(create_part("mixer", PartSpec("ssd", params), name="m"), "bfloat16", max_tokens=1024, pages=8, seed=13)
     g = torch.Generator().manual_seed(14)
     x_of = {"a": torch.randn(700, 40, generator=g).to(torch.bfloat16), "b": torch.randn(3, 40, generator=g).to(torch.bfloat16)}
