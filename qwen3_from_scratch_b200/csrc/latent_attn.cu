@@ -82,23 +82,44 @@ __global__ void latent_kv_post_kernel(const T* __restrict__ proj, int ld, int q_
     r_pages[slot * rot + i] = from_float<T>(rotated(row + kv_col + rank, i, dims, freq, (float)pos, mag));
 }
 
-// One block per token.  q: [T, H, dn + rot] -> q_plain [T, H * dn] and q_rot [T, H, rot] (rotated).
+// One block per token.  q: [T, H, dn + rot] -> q_plain [T, H * dn] and q_rot [T, H, rot] (rotated).  The token's
+// cosines and sines (dims / 2 of each, times mag) are worked out once per block.
 template <typename T>
 __global__ void latent_q_post_kernel(const T* __restrict__ q, int H, int dn, int rot, int dims,
                                      const float* __restrict__ freq, float mag, const int* __restrict__ positions,
                                      T* __restrict__ q_plain, T* __restrict__ q_rot) {
+  extern __shared__ float cs_table[];  // [dims / 2] cosines, then [dims / 2] sines
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const float pos = (float)positions[t];
+  const int half = dims >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, c;
+    sincosf(pos * freq[i], &sn, &c);
+    cs_table[i] = c * mag;
+    cs_table[half + i] = sn * mag;
+  }
+  __syncthreads();
   const int per = dn + rot;
   const T* row = q + (size_t)t * H * per;
   for (int i = threadIdx.x; i < H * per; i += blockDim.x) {
     const int h = i / per, d = i - h * per;
-    if (d < dn)
+    if (d < dn) {
       q_plain[((size_t)t * H + h) * dn + d] = row[i];
-    else
-      q_rot[((size_t)t * H + h) * rot + (d - dn)] = from_float<T>(rotated(row + (size_t)h * per + dn, d - dn, dims, freq, pos, mag));
+      continue;
+    }
+    const int r = d - dn;
+    const T* v = row + (size_t)h * per + dn;
+    float out;
+    if (r >= dims) {
+      out = to_float(v[r]);
+    } else {
+      const int p = r < half ? r : r - half;
+      const float a = to_float(v[p]), b = to_float(v[p + half]), c = cs_table[p], sn = cs_table[half + p];
+      out = r < half ? a * c - b * sn : b * c + a * sn;
+    }
+    q_rot[((size_t)t * H + h) * rot + r] = from_float<T>(out);
   }
 }
 
@@ -215,8 +236,9 @@ extern "C" int q3_latent_q_post(const void* q, int H, int dn, int rot, int dims,
                                 const int* positions, void* q_plain, void* q_rot, int dtype, int T, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || dn <= 0 || rot < 0 || dims < 0 || dims > rot || dims % 2) return Q3_ERR_SIZE;
-  Q3_BY_DTYPE(dtype, q3::launch(q3::latent_q_post_kernel<E>, dim3(T), dim3(128), 0, stream, (const E*)q, H, dn, rot, dims,
-                                freq, mag, positions, (E*)q_plain, (E*)q_rot))
+  if (dims > 8192) return Q3_ERR_SIZE;
+  Q3_BY_DTYPE(dtype, q3::launch(q3::latent_q_post_kernel<E>, dim3(T), dim3(256), (size_t)dims * sizeof(float), stream,
+                                (const E*)q, H, dn, rot, dims, freq, mag, positions, (E*)q_plain, (E*)q_rot))
   return q3::launch_status();
 }
 

@@ -4,7 +4,7 @@
 // serves all heads and all tokens of a request's portion.
 //
 // Rows are (token, head) pairs of one request, sixteen to a row group; a row group is four warps.  Per tile of
-// LM_KT keys:
+// LM_KT keys (32, or 16 in the form for single tokens):
 //   scores   the reduction over the rank + rot key values is cut into four ranges, one per warp, whose slice of
 //            the queries stays in registers as A fragments for the whole kernel (a row group reads a key tile
 //            once, not once per warp); the four partial score tiles meet in shared memory and every warp sums them
@@ -19,7 +19,6 @@
 
 namespace q3 {
 
-constexpr int LM_KT = 32;  // keys per tile
 
 __device__ __forceinline__ float lm_exp2(float x) {  // 2^x by the hardware's unit; 2^-inf = 0
   float y;
@@ -28,8 +27,9 @@ __device__ __forceinline__ float lm_exp2(float x) {  // 2^x by the hardware's un
 }
 
 // KS: k-steps of 16 per warp in the scores (rank + rot padded to 64 * KS); NO: pairs of 8-column output tiles per
-// warp (rank = 64 * NO); RG: row groups per block.
-template <int KS, int NO, int RG>
+// warp (rank = 64 * NO); RG: row groups per block; LM_KT: keys per tile (32 for two row groups; 16 for one, the form of
+// single tokens, whose blocks are bound by the latency of their tiles: the smaller tile lets an SM hold four).
+template <int KS, int NO, int RG, int LM_KT>
 __global__ void __launch_bounds__(RG * 128, RG == 2 ? 2 : 4)
 latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ q_rot,
                        const __nv_bfloat16* __restrict__ c_pages, const __nv_bfloat16* __restrict__ r_pages,
@@ -286,16 +286,16 @@ static int lm_launch(const float* q_abs, const void* q_rot, const void* c_pages,
                      float* partial, int T, int B, int max_q_len, int H, int rank, int rot, float scale, int splits,
                      int* status, cudaStream_t stream) {
   using bf16 = __nv_bfloat16;
-  constexpr int PITCH = 64 * KS + 8;
+  constexpr int PITCH = 64 * KS + 8, LM_KT = RG == 2 ? 32 : 16;
   const size_t smem = (size_t)2 * LM_KT * PITCH * sizeof(bf16) + (size_t)RG * 4 * 16 * LM_KT * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(latent_attn_mma_kernel<KS, NO, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(latent_attn_mma_kernel<KS, NO, RG, RG == 2 ? 32 : 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     configured = true;
   }
   const long long tiles = ((long long)max_q_len * H + 16 * RG - 1) / (16 * RG);
   if (tiles > 65535 || splits > 65535) return Q3_ERR_SIZE;
-  launch(latent_attn_mma_kernel<KS, NO, RG>, dim3(B, (unsigned)tiles, splits), dim3(RG * 128), smem, stream, q_abs,
+  launch(latent_attn_mma_kernel<KS, NO, RG, RG == 2 ? 32 : 16>, dim3(B, (unsigned)tiles, splits), dim3(RG * 128), smem, stream, q_abs,
          (const bf16*)q_rot, (const bf16*)c_pages, (const bf16*)r_pages, q_start, kv_len, table, stride, page_size,
          num_pages, (bf16*)out, partial, T, H, rank, rot, scale * 1.4426950408889634f, splits, page_shift_of(page_size),
          status);

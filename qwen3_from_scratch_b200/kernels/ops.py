@@ -1572,7 +1572,7 @@ def gated_group_norm(y: torch.Tensor, z: torch.Tensor, z_col: int, weight: torch
 
 
 LATENT_MAX_SPLITS = 16  # key ranges per request of the single-token form
-LATENT_SPLIT_TILES = 4   # a range is at least so many tiles of 32 keys
+LATENT_SPLIT_TILES = 4   # a range is at least so many times 32 keys
 
 
 def latent_attention_fast(dtype: torch.dtype, rank: int, rot: int) -> bool:
@@ -1586,11 +1586,12 @@ def latent_partial_numel(num_seqs: int, heads: int, rank: int) -> int:
 
 
 def latent_decode_splits(num_seqs: int, heads: int, max_kv_len: int) -> int:
-    """Key ranges per request when every row brings one token: enough blocks to fill the device twice, a range no
-    shorter than ``LATENT_SPLIT_TILES`` tiles."""
+    """Key ranges per request when every row brings one token: enough blocks for the four that an SM holds at a
+    time (a block of four warps leaves most of the latency of its tile uncovered), a range no shorter than
+    ``LATENT_SPLIT_TILES`` tiles."""
     blocks = num_seqs * -(-heads // 16)
     by_length = max(1, -(-max_kv_len // 32) // LATENT_SPLIT_TILES)
-    return max(1, min(LATENT_MAX_SPLITS, by_length, -(-2 * sm_count() // blocks)))
+    return max(1, min(LATENT_MAX_SPLITS, by_length, -(-4 * sm_count() // blocks)))
 
 
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor, r_pages: torch.Tensor, ctx,

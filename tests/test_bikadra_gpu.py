@@ -42,7 +42,8 @@ def close(got, want, dtype, what="", tol=None):
 
 # ---------------------------------------------------------------------- the small kernels against float32 torch
 @pytest.mark.parametrize("dtype", list(DT))
-@pytest.mark.parametrize("S,W,T", [(1, 48, 5), (2, 64, 33), (3, 200, 7), (4, 1024, 19), (8, 96, 3)])
+@pytest.mark.parametrize("S,W,T", [(1, 48, 5), (2, 64, 33), (3, 200, 7), (4, 1024, 19), (8, 96, 3), (2, 50, 4), (3, 201, 6),
+                                   (2, 5000, 3)])
 def test_stream_kernels(S, W, T, dtype):
     """Reading S streams into a norm with and without an open write, and the last norm over chosen rows."""
     from qwen3_from_scratch_b200.kernels import ops
@@ -102,7 +103,7 @@ def test_scaled_embedding_softcap_and_activation():
 
 
 @pytest.mark.parametrize("dtype", list(DT))
-@pytest.mark.parametrize("I,parts", [(48, 1), (96, 3), (512, 2), (40, 40)])
+@pytest.mark.parametrize("I,parts", [(48, 1), (96, 3), (512, 2), (40, 40), (6000, 2)])
 def test_gated_norm_in_parts(I, parts, dtype):
     from qwen3_from_scratch_b200.kernels import ops
     g = torch.Generator().manual_seed(I)
