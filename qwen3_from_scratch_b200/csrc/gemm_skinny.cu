@@ -69,6 +69,7 @@ struct SkinnyFuse {
   __nv_bfloat16* scaled_out;  // [T, N]: the new rows times that weight, the operand of a NORMED product
   int early;            // EPI 2: the stream may be read ahead of the wait (the launch before did not write it)
   int gate_act;         // EPI 1: the gate's activation, a Q3_ACT_* code (0: SiLU)
+  int plain_act;        // EPI 0: 0, or 1 + a Q3_ACT_* code applied to every result (a feed-forward without a gate)
 };
 
 constexpr int GS_SS_ROWS = 16;  // row pitch of the partial sums
@@ -222,6 +223,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 #pragma unroll
       for (int s = 0; s < WK; ++s) v += red[warp + s][f][tok];
       if (NORMED) v *= rs_s[tok];
+      if (fuse.plain_act) v = activate(v, fuse.plain_act - 1);
       out[(size_t)tok * ldo + row0 + f] = from_float<OutT>(v);
     }
   } else if (EPI == 2) {
@@ -323,14 +325,26 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
 
 // out[T, N] (row pitch ldo) = X[T, K] * W[N, K]^T for T <= 16; X, W bfloat16, K a multiple of 8.
 // out_f32 != 0: float32 output, else bfloat16.  swiglu != 0: W's rows alternate gate/up in blocks of
-// eight, N is a multiple of 16 and out is [T, N / 2]; the gate's activation is Q3_ACT code swiglu - 1.
+// eight, N is a multiple of 16 and out is [T, N / 2]; the gate's activation is Q3_ACT code swiglu - 1.  swiglu < 0: no
+// gate, every result goes through the activation Q3_ACT code -swiglu - 1 before it is stored.
 extern "C" int q3_gemm_skinny(const void* X, const void* W, void* out, int T, int N, int K, int ldo, int out_f32,
                               int swiglu, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (T > 16 || K <= 0 || K % 8 || swiglu < 0 || swiglu > 1 + Q3_ACT_GELU_TANH || (swiglu && (N % 16 || out_f32)))
+  if (T > 16 || K <= 0 || K % 8 || swiglu < -1 - Q3_ACT_GELU_TANH || swiglu > 1 + Q3_ACT_GELU_TANH ||
+      (swiglu > 0 && (N % 16 || out_f32)))
     return Q3_ERR_SIZE;
   if ((uintptr_t)X % 16 || (uintptr_t)W % 16) return Q3_ERR_ALIGN;
   using bf16 = __nv_bfloat16;
+  if (swiglu < 0) {  // no gate: the activation Q3_ACT code -swiglu - 1 on every result
+    q3::SkinnyFuse fuse{};
+    fuse.plain_act = -swiglu;
+    if (out_f32) {
+      if (T <= 8) return q3::gemm_skinny_launch<1, 0, float>(X, W, out, T, N, K, ldo, stream, fuse);
+      return q3::gemm_skinny_launch<2, 0, float>(X, W, out, T, N, K, ldo, stream, fuse);
+    }
+    if (T <= 8) return q3::gemm_skinny_launch<1, 0, bf16>(X, W, out, T, N, K, ldo, stream, fuse);
+    return q3::gemm_skinny_launch<2, 0, bf16>(X, W, out, T, N, K, ldo, stream, fuse);
+  }
   if (swiglu) {
     q3::SkinnyFuse fuse{};
     fuse.gate_act = swiglu - 1;

@@ -255,28 +255,37 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
   }
 }
 
-// One block per (token, head): the key ranges' partial results added up in the order of the ranges.
+// One block per (token, head): the key ranges' partial results added up in the order of the ranges.  A range's
+// weight, 2^(its maximum - the row's maximum) / the row's sum, is worked out once per block.
+constexpr int LM_MAX_SPLITS = 64;
+
 __global__ void latent_attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int rank,
                                          int splits) {
+  __shared__ float weight[LM_MAX_SPLITS];
   pdl_wait();
   pdl_launch_dependents();
   const size_t row = blockIdx.x;
   const float* p = partial + row * splits * (rank + 2);
-  float mx = -INFINITY;
-  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, p[(size_t)s * (rank + 2)]);
-  float total = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = p[(size_t)s * (rank + 2)];
-    if (ms != -INFINITY) total += p[(size_t)s * (rank + 2) + 1] * exp2f(ms - mx);
-  }
-  const float inv = total > 0.f ? 1.0f / total : 0.f;
-  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
-    float acc = 0.f;
+  if (threadIdx.x < 32) {
+    float mx = -INFINITY;
+    for (int s = threadIdx.x; s < splits; s += 32) mx = fmaxf(mx, p[(size_t)s * (rank + 2)]);
+    mx = warp_max(mx);
+    float total = 0.f;  // every lane adds all ranges in their order: the same sum in every lane
     for (int s = 0; s < splits; ++s) {
       const float ms = p[(size_t)s * (rank + 2)];
-      if (ms != -INFINITY) acc += p[(size_t)s * (rank + 2) + 2 + d] * exp2f(ms - mx);
+      if (ms != -INFINITY) total += p[(size_t)s * (rank + 2) + 1] * lm_exp2(ms - mx);
     }
-    out[row * rank + d] = __float2bfloat16_rn(acc * inv);
+    const float inv = total > 0.f ? 1.0f / total : 0.f;
+    for (int s = threadIdx.x; s < splits; s += 32) {
+      const float ms = p[(size_t)s * (rank + 2)];
+      weight[s] = ms != -INFINITY ? lm_exp2(ms - mx) * inv : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc = fmaf(p[(size_t)s * (rank + 2) + 2 + d], weight[s], acc);
+    out[row * rank + d] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -294,7 +303,7 @@ static int lm_launch(const float* q_abs, const void* q_rot, const void* c_pages,
     configured = true;
   }
   const long long tiles = ((long long)max_q_len * H + 16 * RG - 1) / (16 * RG);
-  if (tiles > 65535 || splits > 65535) return Q3_ERR_SIZE;
+  if (tiles > 65535 || splits > LM_MAX_SPLITS) return Q3_ERR_SIZE;
   launch(latent_attn_mma_kernel<KS, NO, RG, RG == 2 ? 32 : 16>, dim3(B, (unsigned)tiles, splits), dim3(RG * 128), smem, stream, q_abs,
          (const bf16*)q_rot, (const bf16*)c_pages, (const bf16*)r_pages, q_start, kv_len, table, stride, page_size,
          num_pages, (bf16*)out, partial, T, H, rank, rot, scale * 1.4426950408889634f, splits, page_shift_of(page_size),

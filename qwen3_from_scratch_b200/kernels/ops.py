@@ -492,9 +492,10 @@ def gemm_skinny_takes(rows: int, weight: torch.Tensor) -> bool:
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu_blocks: bool = False,
-                activation: str = "silu") -> None:
+                activation: str = "silu", plain_activation: Optional[str] = None) -> None:
     """out[T, N] = x[T, K] @ w[N, K]^T for T <= 16, bfloat16 in, out bfloat16 or float32.
-    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [T, N / 2] = up * act(gate)."""
+    ``swiglu_blocks``: w's rows alternate gate/up in blocks of eight and out is [T, N / 2] = up * act(gate).
+    ``plain_activation`` (without ``swiglu_blocks``): out = act(x w^T), the activation applied before the store."""
     _check("gemm_skinny.x", x, torch.bfloat16)
     _check("gemm_skinny.w", w, torch.bfloat16)
     _check("gemm_skinny.out", out)
@@ -505,7 +506,9 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu_bloc
         raise KernelError(f"gemm_skinny: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
     code = library().q3_gemm_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, want_cols,
                                     1 if out.dtype == torch.float32 else 0,
-                                    1 + activation_code(activation, gate=True) if swiglu_blocks else 0, _stream())
+                                    1 + activation_code(activation, gate=True) if swiglu_blocks else (
+                                        -1 - activation_code(plain_activation, gate=True) if plain_activation else 0),
+                                    _stream())
     _done("gemm_skinny", code, f"T {T} N {N} K {K}")
 
 
@@ -1571,7 +1574,7 @@ def gated_group_norm(y: torch.Tensor, z: torch.Tensor, z_col: int, weight: torch
     _done("gated_group_norm", code, f"{parts} parts of {I}")
 
 
-LATENT_MAX_SPLITS = 16  # key ranges per request of the single-token form
+LATENT_MAX_SPLITS = 32  # key ranges per request of the single-token form
 LATENT_SPLIT_TILES = 4   # a range is at least so many times 32 keys
 
 
@@ -1586,12 +1589,14 @@ def latent_partial_numel(num_seqs: int, heads: int, rank: int) -> int:
 
 
 def latent_decode_splits(num_seqs: int, heads: int, max_kv_len: int) -> int:
-    """Key ranges per request when every row brings one token: enough blocks for the four that an SM holds at a
-    time (a block of four warps leaves most of the latency of its tile uncovered), a range no shorter than
-    ``LATENT_SPLIT_TILES`` tiles."""
+    """Key ranges per request when every row brings one token.  A block takes about 1.6 us per 16-key tile whatever
+    else runs (its tile's latency and a chain of dependent steps), and every range costs the merge a pass: as many
+    ranges as fill the four places an SM has for these blocks, none shorter than ``LATENT_SPLIT_TILES`` x 32 keys
+    (measured: 8 requests over 2,048 keys 211 us in one range, 44 in 16; 64 requests 71 us in 8 ranges, 93 in 16;
+    8 requests over 16,384 keys 128 us in 16 ranges, 99 in 32)."""
     blocks = num_seqs * -(-heads // 16)
     by_length = max(1, -(-max_kv_len // 32) // LATENT_SPLIT_TILES)
-    return max(1, min(LATENT_MAX_SPLITS, by_length, -(-4 * sm_count() // blocks)))
+    return max(1, min(LATENT_MAX_SPLITS, by_length, 4 * sm_count() // blocks))
 
 
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor, r_pages: torch.Tensor, ctx,

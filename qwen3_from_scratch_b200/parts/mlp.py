@@ -123,6 +123,13 @@ class DenseMLP(FeedForward):
         self.down = Linear(weights.pop(self.tensors["down"]), rt, tag="ffn.down")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        rows = x.shape[0]
+        if (ops.gemm_skinny_takes(rows, self.up.weight) and x.dtype == torch.bfloat16
+                and self.up.out_dtype == torch.bfloat16):
+            # decoding: the weight is streamed once and the activation applied before the store
+            h = self.up._buffer("_out", rows, self.up.out_dtype)
+            ops.gemm_skinny(x, self.up.weight, h, plain_activation=self.activation)
+            return self.down(h)
         h = self.up(x)
         ops.act(h, h, self.activation)
         return self.down(h)

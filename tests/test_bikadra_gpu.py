@@ -14,7 +14,7 @@ import torch
 import plain_bikadra as plain
 from bikadra_models import CONFIGS, latent, make_folder, mamba2
 from harness import Replayer, assert_close
-from test_binupel_gpu import MixerBench
+from test_binupel_gpu import MixerBench, part_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -115,6 +115,22 @@ def test_gated_norm_in_parts(I, parts, dtype):
     v = y.double() * plain.silu(z[:, 4:4 + I].double())
     want = plain.unit_rms(v.view(9, parts, I // parts), 1e-5).reshape(9, I) * weight.double()
     close(out, want, dtype, "gated norm", tol=1e-5 if dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("rows", [3, 12, 40, 300])
+def test_dense_feed_forward_in_every_product(rows, dtype):
+    """W_down gelu_tanh(W_up x): a few rows (the activation in the few-rows product's epilogue) and many."""
+    from qwen3_from_scratch_b200.parts.base import PartSpec, Runtime
+    from qwen3_from_scratch_b200.registry import create_part
+    part = create_part("feed_forward", PartSpec("dense_mlp", {"hidden_size": 64, "intermediate_size": 136,
+                                                              "activation": "gelu_tanh", "names": {"up": "up", "down": "down"}}),
+                       name="f")
+    dev, ref = part_weights(part, dtype, seed=rows)
+    part.setup(Runtime(torch.device("cuda:0"), DT[dtype], 512, 2), dict(dev))
+    x = torch.randn(rows, 64, generator=torch.Generator().manual_seed(rows + 1)).to(DT[dtype])
+    want = plain.dense_ff(x.double(), ref, "")
+    close(part.forward(x.cuda()), want, dtype, f"dense feed-forward, {rows} rows")
 
 
 # ---------------------------------------------------------------------- each mixer alone
