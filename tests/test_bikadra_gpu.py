@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import plain_bikadra as plain
-from bikadra_models import CONFIGS, latent, make_folder, mamba2
+from bikadra_models import CONFIGS, make_folder
 from harness import Replayer, assert_close
 from test_binupel_gpu import MixerBench, part_weights
 
