@@ -171,6 +171,9 @@ def mixers():
         # one group, one norm part, a single tap, a state that one lane holds
         "ssd, one of each": {"hidden_size": 40, "num_heads": 3, "vdim": 16, "state": 8, "groups": 1, "norm_groups": 1,
                              "conv": 1, "norm_eps": 1e-6},
+        # heads whose channels are no multiple of four (a channel per thread), a state of 20, five norm parts
+        "ssd, odd channels": {"hidden_size": 40, "num_heads": 3, "vdim": 10, "state": 20, "groups": 3, "norm_groups": 5,
+                              "conv": 2, "norm_eps": 1e-5},
         # a state spread over eight lanes, as many groups as heads, five taps
         "ssd, wide state": {"hidden_size": 40, "num_heads": 2, "vdim": 12, "state": 100, "groups": 2, "norm_groups": 3,
                             "conv": 5, "norm_eps": 1e-5},
@@ -179,7 +182,7 @@ def mixers():
 
 
 MIXER_KINDS = ["latent_attention", "latent_attention, one head", "latent_attention, many heads", "ssd",
-               "ssd, one of each", "ssd, wide state"]
+               "ssd, one of each", "ssd, wide state", "ssd, odd channels"]
 
 
 @pytest.mark.parametrize("dtype", list(DT))
@@ -206,8 +209,8 @@ def test_mixer_alone_whole_in_portions_and_beside_another_request(kind, dtype):
         close(torch.cat(got[r]), want[r], dtype, f"{kind} portions {r}")
 
 
-@pytest.mark.parametrize("kind", ["ssd", "ssd, wide state", "ssd, three lanes of states", "ssd, matrix form 64",
-                                  "ssd, matrix form 128"])
+@pytest.mark.parametrize("kind", ["ssd", "ssd, wide state", "ssd, odd channels", "ssd, three lanes of states",
+                                  "ssd, matrix form 64", "ssd, matrix form 128"])
 def test_long_portions_run_in_chunks_and_leave_the_same_state(kind):
     """bfloat16: a portion of several hundred tokens is cut into chunks that run side by side, a short one is
     walked in one piece; a long portion beside a single token of another request, then the same tokens in short
